@@ -44,7 +44,7 @@ class PagedGroup:
     spec: PagedKV
     members: list                     # cache slot indices, in order
     pool: PagePool
-    kv: torch.Tensor | None           # [members, 2, Hkv, pages, block, hd]
+    kv: torch.Tensor | None           # [members, 2 (1 if shared_kv), Hkv, pages, block, hd]
     table: np.ndarray                 # [max_requests, max_blocks] int32, -1 = none
 
 
@@ -103,8 +103,10 @@ class CacheManager:
             grp.members.append(slot)
         if allocate:
             for g in self.paged:
+                # one pool a member where keys and values are the same cached vector
                 g.kv = torch.zeros(
-                    (len(g.members), 2, g.spec.n_kv_heads, self.num_blocks,
+                    (len(g.members), 1 if getattr(g.spec, "shared_kv", False) else 2,
+                     g.spec.n_kv_heads, self.num_blocks,
                      self.block_size, g.spec.head_dim),
                     device=device, dtype=kv_dtype)
             for g in self.fixed:
@@ -122,7 +124,7 @@ class CacheManager:
                 out.append(CacheHandle(
                     kind="paged", group=gid,
                     k_pool=None if g.kv is None else g.kv[m, 0],
-                    v_pool=None if g.kv is None else g.kv[m, 1],
+                    v_pool=None if g.kv is None else g.kv[m, g.kv.shape[1] - 1],
                     window=g.spec.window))
             elif kind == "fixed":
                 g = self.fixed[gid]
@@ -375,5 +377,5 @@ class CacheManager:
                 vs.append(nan)
             else:
                 ks.append(g.kv[m, 0, :, p, :take])
-                vs.append(g.kv[m, 1, :, p, :take])
+                vs.append(g.kv[m, g.kv.shape[1] - 1, :, p, :take])
         return torch.cat(ks, dim=1), torch.cat(vs, dim=1)

@@ -1,5 +1,6 @@
 from .model_config import (ConfigError, DenseLlamaConfig, canonical_dtype_name,
                            read_config_json, write_config_json)
+from .zededra_config import ZededraConfig
 from .engine_options import EngineOptions
 from .registry import (register_architecture, unregister_architecture,
                        lookup_architecture, architecture_names, config_from_dict,

@@ -1,0 +1,292 @@
+// Routed experts: choose, sort, multiply expert by expert, add up.
+//
+// mls_route_topk: scores s = sigmoid(z) of float32 router logits z [T, E]; for every
+//   token the `top` largest scores (the lowest index wins a tie) with the scores
+//   themselves as weights (optionally renormalised to sum 1).  A (token, choice) pair is
+//   a "slot": slot = t * top + j.
+// mls_route_sort: slots ordered by expert: order[p] = slot, offsets[E + 1], and the list
+//   of row tiles (tile_expert, tile_row0) the products below walk.  One CTA.
+// mls_expert_glu: y[p, :] = silu(Wg[e] a) * (Wu[e] a) with a = weight[slot] * h[token]
+//   (input scaling: the weight multiplies what enters the expert) or a = h[token]
+//   (output scaling, applied by the down product instead).
+// mls_expert_down: per_slot[slot, :] = Wd[e] y[p, :] (times the weight with output
+//   scaling), float32.
+// mls_expert_combine: delta[t] = sum_j per_slot[t * top + j] + shared[t], j ascending.
+//
+// The products run on CUDA cores with float32 accumulation over k ascending, one row
+// tile of one expert a CTA; every row is computed by itself, so a token's result does
+// not depend on the batch, on its place in the sorted order or on the other tokens of
+// its expert.
+#include "common.cuh"
+
+namespace {
+constexpr int BM = 32, BN = 64, BK = 16, TM = 2, TN = 4;   // 256 threads
+
+__global__ void route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts,
+                                  int top, int renorm, int* __restrict__ idx,
+                                  float* __restrict__ weight) {
+    chain_release();
+    chain_wait();
+    // one warp a token
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= n_tokens) return;
+    const float* z = logits + (size_t)t * n_experts;
+    float total = 0.f;
+    for (int j = 0; j < top; ++j) {
+        float best = -1.f;
+        int arg = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32) {
+            bool taken = false;
+            for (int p = 0; p < j; ++p) taken |= idx[(size_t)t * top + p] == e;
+            const float s = 1.0f / (1.0f + expf(-z[e]));
+            if (!taken && (s > best || (s == best && e < arg))) {
+                best = s;
+                arg = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ob > best || (ob == best && oa < arg)) {
+                best = ob;
+                arg = oa;
+            }
+        }
+        if (arg >= n_experts) {                  // only scores that are not numbers were left
+            arg = 0;
+            best = 0.f;
+        }
+        if (lane == 0) {
+            idx[(size_t)t * top + j] = arg;
+            weight[(size_t)t * top + j] = best;
+        }
+        total += best;
+        __syncwarp();
+    }
+    if (renorm && lane == 0)
+        for (int j = 0; j < top; ++j) weight[(size_t)t * top + j] /= total;
+}
+
+__global__ void __launch_bounds__(1024)
+route_sort_kernel(const int* __restrict__ idx, int n_slots, int n_experts,
+                  int* __restrict__ order, int* __restrict__ offsets,
+                  int* __restrict__ tile_expert, int* __restrict__ tile_row0, int max_tiles,
+                  int* __restrict__ cursor /* [E] scratch */) {
+    chain_release();
+    chain_wait();
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) cursor[e] = 0;
+    __syncthreads();
+    for (int s = threadIdx.x; s < n_slots; s += blockDim.x) atomicAdd(&cursor[idx[s]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tile = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            const int c = cursor[e];
+            offsets[e] = at;
+            for (int r = 0; r < c && tile < max_tiles; r += BM) {
+                tile_expert[tile] = e;
+                tile_row0[tile] = at + r;
+                ++tile;
+            }
+            cursor[e] = at;
+            at += c;
+        }
+        offsets[n_experts] = at;
+        for (; tile < max_tiles; ++tile) tile_expert[tile] = -1;
+    }
+    __syncthreads();
+    // which place a slot gets inside its expert is left to the atomics: every row is
+    // computed by itself, so the values do not depend on it
+    for (int s = threadIdx.x; s < n_slots; s += blockDim.x)
+        order[atomicAdd(&cursor[idx[s]], 1)] = s;
+}
+
+// GLU: A row = h[slot / top] (* weight[slot] if scale_in), W = [gate rows | up rows] of
+// expert e ([2F, K]), out y[p, n] = silu(gate) * up in T.
+// !GLU: A row = y[p], W = Wd[e] ([N, K]), out per_slot[slot, n] float32 (* weight[slot]
+// if scale_out).
+template <typename T, bool GLU>
+__global__ void __launch_bounds__(256)
+expert_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __restrict__ out,
+                   const int* __restrict__ order, const int* __restrict__ offsets,
+                   const int* __restrict__ tile_expert, const int* __restrict__ tile_row0,
+                   const float* __restrict__ weight, int top, int scale, int N, int K) {
+    chain_release();
+    chain_wait();
+    const int e = tile_expert[blockIdx.y];
+    if (e < 0) return;
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    __shared__ float Us[GLU ? BK : 1][BN + 4];
+    __shared__ int slot_s[BM];
+    const int tid = threadIdx.x;
+    const int p0 = tile_row0[blockIdx.y], p_end = offsets[e + 1];
+    const int n0 = blockIdx.x * BN;
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);      // 16 x 16
+    if (tid < BM) slot_s[tid] = p0 + tid < p_end ? order[p0 + tid] : -1;
+    __syncthreads();
+    const T* We = W + (size_t)e * (GLU ? 2 : 1) * N * K;
+    float acc[TM][TN], acu[GLU ? TM : 1][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            acc[i][j] = 0.f;
+            if (GLU) acu[i][j] = 0.f;
+        }
+    // A tile: 32 rows x 16 k = 512 values, two a thread; W tile: 64 rows x 16 k, four a thread
+    const int arow = tid >> 3, ak = (tid & 7) * 2;
+    const int wrow = tid >> 2, wk = (tid & 3) * 4;
+    const int aslot = slot_s[arow];
+    const T* arow_p = nullptr;
+    float ascale = 1.f;
+    if (aslot >= 0) {
+        if (GLU) {
+            arow_p = A + (size_t)(aslot / top) * K;
+            if (scale) ascale = weight[aslot];
+        } else {
+            arow_p = A + (size_t)(p0 + arow) * K;
+        }
+    }
+    for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            const int k = k0 + ak + x;
+            As[ak + x][arow] = (arow_p && k < K) ? Elem<T>::load(arow_p + k) * ascale : 0.f;
+        }
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+            const int k = k0 + wk + x, n = n0 + wrow;
+            const bool ok = n < N && k < K;
+            Ws[wk + x][wrow] = ok ? Elem<T>::load(We + (size_t)n * K + k) : 0.f;
+            if (GLU) Us[wk + x][wrow] = ok ? Elem<T>::load(We + (size_t)(N + n) * K + k) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[TM], w[TN], u[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) {
+                w[j] = Ws[kk][tx * TN + j];
+                if (GLU) u[j] = Us[kk][tx * TN + j];
+            }
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) {
+                    acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+                    if (GLU) acu[i][j] = fmaf(a[i], u[j], acu[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int r = ty * TM + i;
+        const int slot = slot_s[r];
+        if (slot < 0) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tx * TN + j;
+            if (n >= N) continue;
+            if (GLU) {
+                const float g = acc[i][j];
+                Elem<T>::store((T*)out + (size_t)(p0 + r) * N + n,
+                               (g / (1.0f + expf(-g))) * acu[i][j]);
+            } else {
+                ((float*)out)[(size_t)slot * N + n] = scale ? acc[i][j] * weight[slot] : acc[i][j];
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void expert_combine_kernel(const float* __restrict__ per_slot, int top,
+                                      const void* __restrict__ shared, int shared_dtype,
+                                      T* __restrict__ delta, size_t n, int d) {
+    chain_release();
+    chain_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = i / d, c = i - t * d;
+        float s = 0.f;
+        for (int j = 0; j < top; ++j) s += per_slot[(t * top + j) * d + c];
+        if (shared) s += load_as_float(shared, i, shared_dtype);
+        Elem<T>::store(delta + i, s);
+    }
+}
+}  // namespace
+
+MLS_API int mls_expert_tile_rows() { return BM; }
+
+MLS_API int mls_route_topk(const float* logits, int n_tokens, int n_experts, int top, int renorm,
+                           int* idx, float* weight, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (top <= 0 || top > n_experts) return MLS_ERR_UNSUPPORTED;
+    MLS_LAUNCH((route_topk_kernel), dim3((n_tokens + 3) / 4), dim3(128), 0, stream, logits,
+               n_tokens, n_experts, top, renorm, idx, weight);
+    return launch_status();
+}
+
+MLS_API int mls_route_sort(const int* idx, int n_slots, int n_experts, int* order, int* offsets,
+                           int* tile_expert, int* tile_row0, int max_tiles, int* cursor,
+                           cudaStream_t stream) {
+    if (n_slots <= 0) return 0;
+    MLS_LAUNCH((route_sort_kernel), dim3(1), dim3(1024), 0, stream, idx, n_slots, n_experts, order,
+               offsets, tile_expert, tile_row0, max_tiles, cursor);
+    return launch_status();
+}
+
+MLS_API int mls_expert_glu(const void* h, const void* w_gate_up, void* y, int dtype,
+                           const int* order, const int* offsets, const int* tile_expert,
+                           const int* tile_row0, int max_tiles, const float* weight, int top,
+                           int scale_in, int F, int K, cudaStream_t stream) {
+    if (max_tiles <= 0) return 0;
+    dim3 grid((F + BN - 1) / BN, max_tiles);
+    if (dtype == MLS_BF16)
+        MLS_LAUNCH((expert_gemm_kernel<__nv_bfloat16, true>), dim3(grid), dim3(256), 0, stream,
+                   (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gate_up, y, order, offsets,
+                   tile_expert, tile_row0, weight, top, scale_in, F, K);
+    else
+        MLS_LAUNCH((expert_gemm_kernel<float, true>), dim3(grid), dim3(256), 0, stream,
+                   (const float*)h, (const float*)w_gate_up, y, order, offsets, tile_expert,
+                   tile_row0, weight, top, scale_in, F, K);
+    return launch_status();
+}
+
+MLS_API int mls_expert_down(const void* y, const void* w_down, float* per_slot, int dtype,
+                            const int* order, const int* offsets, const int* tile_expert,
+                            const int* tile_row0, int max_tiles, const float* weight, int top,
+                            int scale_out, int D, int F, cudaStream_t stream) {
+    if (max_tiles <= 0) return 0;
+    dim3 grid((D + BN - 1) / BN, max_tiles);
+    if (dtype == MLS_BF16)
+        MLS_LAUNCH((expert_gemm_kernel<__nv_bfloat16, false>), dim3(grid), dim3(256), 0, stream,
+                   (const __nv_bfloat16*)y, (const __nv_bfloat16*)w_down, (void*)per_slot, order,
+                   offsets, tile_expert, tile_row0, weight, top, scale_out, D, F);
+    else
+        MLS_LAUNCH((expert_gemm_kernel<float, false>), dim3(grid), dim3(256), 0, stream,
+                   (const float*)y, (const float*)w_down, (void*)per_slot, order, offsets,
+                   tile_expert, tile_row0, weight, top, scale_out, D, F);
+    return launch_status();
+}
+
+MLS_API int mls_expert_combine(const float* per_slot, int top, const void* shared,
+                               int shared_dtype, void* delta, int dtype, int n_tokens, int d,
+                               cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const size_t n = (size_t)n_tokens * d;
+    const size_t want = (n + 255) / 256;
+    const int blocks = (int)(want < (size_t)(8 * sm_count()) ? want : 8 * sm_count());
+    if (dtype == MLS_BF16)
+        MLS_LAUNCH((expert_combine_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream,
+                   per_slot, top, shared, shared_dtype, (__nv_bfloat16*)delta, n, d);
+    else
+        MLS_LAUNCH((expert_combine_kernel<float>), dim3(blocks), dim3(256), 0, stream, per_slot,
+                   top, shared, shared_dtype, (float*)delta, n, d);
+    return launch_status();
+}

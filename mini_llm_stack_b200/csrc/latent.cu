@@ -1,0 +1,152 @@
+// Latent attention: the normalised latents of a step, and the per-head products that
+// let attention run over the cached latent itself.
+//
+// A token caches one latent c [r] (r = latent size): every head's key is W_uk[h] c and
+// its value W_uv[h] c.  Then  q_h . k_h = (W_uk[h]^T q_h) . c  and
+// sum_j p_j v_hj = W_uv[h] (sum_j p_j c_j):  with the query taken into the latent space
+// first and the result taken out of it afterwards, attention is multi-query attention
+// with the latent as the single key AND value head, and the paged kernels run on the
+// latent pool as it is.  Nothing but c is cached and no key or value is rebuilt.
+//
+// mls_latent_norm_store: down [T, rq + r] float32 (the two down projections side by
+//   side).  cq[t] = unit_rms(down[t, :rq]) * wq  (skipped if rq == 0);
+//   c = unit_rms(down[t, rq:]) * wkv goes to the pool at slot_map[t], zero-padded to
+//   the pool's row width rp >= r; the rest of a page the request enters is cleared.
+//   unit_rms(v) = v / sqrt(mean(v^2) + eps), float32 with one rounding at the store.
+//
+// mls_headwise_linear: out[t, h, n] = sum_k in[t, h, k] * W[h, n, k] for every head h
+//   (W [H, N, K], K contiguous), rows and heads of in / out at given strides; float32
+//   accumulation over k ascending, whatever T is: a token's result does not depend on
+//   its batch.
+#include "common.cuh"
+#include "page_tail.cuh"
+
+namespace {
+constexpr int LT_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(LT_THREADS)
+latent_norm_store_kernel(const float* __restrict__ down, int rq, int r, int rp,
+                         const void* __restrict__ wq, const void* __restrict__ wkv, int w_dtype,
+                         float eps, T* __restrict__ cq, const int* __restrict__ slot_map,
+                         T* __restrict__ pool, int block_size, int pool_slots, int* status) {
+    chain_release();
+    chain_wait();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const float* row = down + (size_t)t * (rq + r);
+    if (rq > 0) {
+        float s = 0.f;
+        for (int c = threadIdx.x; c < rq; c += LT_THREADS) s = fmaf(row[c], row[c], s);
+        const float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)rq + eps);
+        for (int c = threadIdx.x; c < rq; c += LT_THREADS)
+            Elem<T>::store(cq + (size_t)t * rq + c, row[c] * inv * load_as_float(wq, c, w_dtype));
+    }
+    const int slot = slot_map[t];
+    const bool slot_ok = slot >= 0 && slot < pool_slots;
+    if (!slot_ok && threadIdx.x == 0 && status) atomicOr(status, MLS_STATUS_BAD_SLOT);
+    float s = 0.f;
+    for (int c = threadIdx.x; c < r; c += LT_THREADS) s = fmaf(row[rq + c], row[rq + c], s);
+    const float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)r + eps);
+    if (!slot_ok) return;
+    T* dst = pool + (size_t)slot * rp;
+    for (int c = threadIdx.x; c < rp; c += LT_THREADS)
+        Elem<T>::store(dst + c, c < r ? row[rq + c] * inv * load_as_float(wkv, c, w_dtype) : 0.f);
+    clear_page_tail<T>(page_tail_to_clear(slot_map, t, gridDim.x, slot, block_size), slot,
+                       block_size, pool_slots / block_size, 1, rp, pool, pool);
+}
+
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;   // 256 threads
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+headwise_linear_kernel(const T* __restrict__ in, long long in_row, long long in_head,
+                       const T* __restrict__ W, T* __restrict__ out, long long out_row,
+                       long long out_head, int M, int N, int K) {
+    chain_release();
+    chain_wait();
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    const int tid = threadIdx.x, head = blockIdx.z;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+    const T* A = in + (size_t)head * in_head;
+    const T* Wh = W + (size_t)head * N * K;
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+    const int lrow = tid >> 2, lk = (tid & 3) * 4;
+    for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int k = k0 + lk + e;
+            const int am = m0 + lrow, wn = n0 + lrow;
+            As[lk + e][lrow] = (am < M && k < K) ? Elem<T>::load(A + (size_t)am * in_row + k) : 0.f;
+            Ws[lk + e][lrow] = (wn < N && k < K) ? Elem<T>::load(Wh + (size_t)wn * K + k) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float a[TM], w[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) w[j] = Ws[kk][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    T* O = out + (size_t)head * out_head;
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int m = m0 + ty * TM + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tx * TN + j;
+            if (n < N) Elem<T>::store(O + (size_t)m * out_row + n, acc[i][j]);
+        }
+    }
+}
+}  // namespace
+
+MLS_API int mls_latent_norm_store(const float* down, int n_tokens, int rq, int r, int rp,
+                                  const void* wq, const void* wkv, int w_dtype, float eps,
+                                  void* cq, int dtype, const int* slot_map, void* pool,
+                                  int block_size, long long pool_slots, int* status,
+                                  cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (r <= 0 || rp < r || rq < 0 || block_size <= 0) return MLS_ERR_UNSUPPORTED;
+    if (dtype == MLS_BF16)
+        MLS_LAUNCH((latent_norm_store_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(LT_THREADS), 0,
+                   stream, down, rq, r, rp, wq, wkv, w_dtype, eps, (__nv_bfloat16*)cq, slot_map,
+                   (__nv_bfloat16*)pool, block_size, (int)pool_slots, status);
+    else
+        MLS_LAUNCH((latent_norm_store_kernel<float>), dim3(n_tokens), dim3(LT_THREADS), 0, stream,
+                   down, rq, r, rp, wq, wkv, w_dtype, eps, (float*)cq, slot_map, (float*)pool,
+                   block_size, (int)pool_slots, status);
+    return launch_status();
+}
+
+MLS_API int mls_headwise_linear(const void* in, long long in_row, long long in_head,
+                                const void* W, void* out, long long out_row, long long out_head,
+                                int dtype, int n_tokens, int n_heads, int N, int K,
+                                cudaStream_t stream) {
+    if (n_tokens <= 0 || n_heads <= 0 || N <= 0) return 0;
+    if (n_heads > 65535) return MLS_ERR_UNSUPPORTED;
+    dim3 grid((N + BN - 1) / BN, (n_tokens + BM - 1) / BM, n_heads);
+    if (dtype == MLS_BF16)
+        MLS_LAUNCH((headwise_linear_kernel<__nv_bfloat16>), dim3(grid), dim3(256), 0, stream,
+                   (const __nv_bfloat16*)in, in_row, in_head, (const __nv_bfloat16*)W,
+                   (__nv_bfloat16*)out, out_row, out_head, n_tokens, N, K);
+    else
+        MLS_LAUNCH((headwise_linear_kernel<float>), dim3(grid), dim3(256), 0, stream,
+                   (const float*)in, in_row, in_head, (const float*)W, (float*)out, out_row,
+                   out_head, n_tokens, N, K);
+    return launch_status();
+}

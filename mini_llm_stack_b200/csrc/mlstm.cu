@@ -1,0 +1,247 @@
+// mLSTM: a matrix memory per head with exponential input and forget gates, carried
+// from token to token in a float32 state slot per request.
+//
+// Per head, with query/key size e and value size f (q pre-scaled by e^-1/2):
+//   i = cap * tanh((zi + bi) / cap)                       log input gate
+//   g = logsigmoid(cap * tanh((zf + bf) / cap))           log forget gate
+//   m' = max(g + m, i)                                    stabiliser, m starts at 0
+//   C' = exp(g + m - m') C + exp(i - m') k v^T            C [e, f]
+//   n' = exp(g + m - m') n + exp(i - m') k                n [e]
+//   num = C'^T q,  den = max(|n' . q|, exp(-m')) + 1e-6
+// mls_mlstm_scan walks the tokens of every request of the step in order, from the state
+// the slot holds, and leaves num [T, H*f] and den [T, H] (float32); the state goes back
+// to the slot.  mls_mlstm_finish then forms o = num / den, divides each head's o by its
+// root mean square (eps inside the root), multiplies by the norm weight and by
+// sigmoid(gate) and rounds once to the activation type.
+//
+// A CTA owns FC columns of one head's C for one request and keeps them in registers:
+// thread (col, eg) holds the rows eg, eg + EG, ... of its column.  Only the CTA of a
+// head's first columns carries n; every CTA carries its own copy of m (the state row
+// of a head is [C (e*f) | n (e) | m (one per column group)]), so no CTA reads what
+// another writes.  All gate arithmetic, the state and the sums are float32; q, k, v and
+// the gate pre-activations come from the projections.  A token's result depends on the
+// tokens before it only through the state, never on the batch or on how the sequence
+// was cut into steps.
+#include "common.cuh"
+
+namespace {
+constexpr int SCAN_THREADS = 256;
+
+__device__ __forceinline__ float soft_cap(float z, float cap) { return cap * tanhf(z / cap); }
+__device__ __forceinline__ float log_sigmoid(float z) {
+    return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+}
+
+// MAXR: most rows of C a thread holds.
+template <typename T, int MAXR>
+__global__ void __launch_bounds__(SCAN_THREADS)
+mlstm_scan_kernel(const T* __restrict__ qkvg, int row_w, int q_off, int k_off, int v_off,
+                  const float* __restrict__ gates /* [T, 2H]: zi | zf */,
+                  const void* __restrict__ bias_i, const void* __restrict__ bias_f, int b_dtype,
+                  float cap, const int* __restrict__ cu_q, const int* __restrict__ state_slot,
+                  float* __restrict__ state, long long slot_stride, int n_heads, int e, int f,
+                  int fc, int n_groups, float* __restrict__ num, float* __restrict__ den) {
+    chain_release();
+    chain_wait();
+    extern __shared__ float sm[];
+    const int grp = blockIdx.x, head = blockIdx.y, req = blockIdx.z;
+    const int eg_count = SCAN_THREADS / fc;
+    const int col = threadIdx.x % fc, eg = threadIdx.x / fc;
+    const bool active = eg < eg_count && grp * fc + col < f;
+    const int gcol = grp * fc + col;
+    const bool first = grp == 0;
+    float* q_s = sm;                       // [e]
+    float* k_s = q_s + e;                  // [e]
+    float* n_s = k_s + e;                  // [e]
+    float* v_s = n_s + e;                  // [fc]
+    float* part = v_s + fc;                // [eg_count][fc]
+    float* red = part + eg_count * fc;     // [33]
+
+    const int t0 = cu_q[req], t1 = cu_q[req + 1];
+    float* st = state + (size_t)state_slot[req] * slot_stride +
+                (size_t)head * ((size_t)e * f + e + n_groups);
+    float C[MAXR];
+#pragma unroll
+    for (int r = 0; r < MAXR; ++r) {
+        const int row = eg + r * eg_count;
+        C[r] = (active && row < e) ? st[(size_t)row * f + gcol] : 0.f;
+    }
+    if (first)
+        for (int i = threadIdx.x; i < e; i += SCAN_THREADS) n_s[i] = st[(size_t)e * f + i];
+    float m = st[(size_t)e * f + e + grp];
+    const float bi = load_as_float(bias_i, head, b_dtype), bf = load_as_float(bias_f, head, b_dtype);
+    const float q_scale = 1.0f / sqrtf((float)e);
+    __syncthreads();
+
+    for (int t = t0; t < t1; ++t) {
+        const T* row = qkvg + (size_t)t * row_w;
+        for (int i = threadIdx.x; i < e; i += SCAN_THREADS) {
+            q_s[i] = Elem<T>::load(row + q_off + head * e + i) * q_scale;
+            k_s[i] = Elem<T>::load(row + k_off + head * e + i);
+        }
+        for (int i = threadIdx.x; i < fc; i += SCAN_THREADS)
+            v_s[i] = grp * fc + i < f ? Elem<T>::load(row + v_off + head * f + grp * fc + i) : 0.f;
+        const float ig = soft_cap(gates[(size_t)t * 2 * n_heads + head] + bi, cap);
+        const float fg = log_sigmoid(soft_cap(gates[(size_t)t * 2 * n_heads + n_heads + head] + bf, cap));
+        const float m_new = fmaxf(fg + m, ig);
+        const float keep = expf(fg + m - m_new), take = expf(ig - m_new);
+        m = m_new;
+        __syncthreads();
+        float o = 0.f;
+        if (active) {
+            const float tv = take * v_s[col];
+#pragma unroll
+            for (int r = 0; r < MAXR; ++r) {
+                const int rr = eg + r * eg_count;
+                if (rr < e) {
+                    C[r] = fmaf(keep, C[r], k_s[rr] * tv);
+                    o = fmaf(C[r], q_s[rr], o);
+                }
+            }
+            part[eg * fc + col] = o;
+        }
+        float nq = 0.f;
+        if (first) {
+            for (int i = threadIdx.x; i < e; i += SCAN_THREADS) {
+                const float nn = fmaf(keep, n_s[i], take * k_s[i]);
+                n_s[i] = nn;
+                nq = fmaf(nn, q_s[i], nq);
+            }
+            nq = block_sum(nq, red);             // also orders part[] before the reads below
+        } else {
+            __syncthreads();
+        }
+        if (eg == 0 && grp * fc + col < f) {
+            float s = 0.f;
+            for (int g2 = 0; g2 < eg_count; ++g2) s += part[g2 * fc + col];
+            num[(size_t)t * n_heads * f + (size_t)head * f + gcol] = s;
+        }
+        if (first && threadIdx.x == 0)
+            den[(size_t)t * n_heads + head] = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < MAXR; ++r) {
+        const int row = eg + r * eg_count;
+        if (active && row < e) st[(size_t)row * f + gcol] = C[r];
+    }
+    if (first)
+        for (int i = threadIdx.x; i < e; i += SCAN_THREADS) st[(size_t)e * f + i] = n_s[i];
+    if (threadIdx.x == 0) st[(size_t)e * f + e + grp] = m;
+}
+
+template <typename T>
+__global__ void mlstm_finish_kernel(const float* __restrict__ num, const float* __restrict__ den,
+                                    const T* __restrict__ gate, int gate_row, int g_off,
+                                    const void* __restrict__ w, int w_dtype, float eps,
+                                    T* __restrict__ out, int n_heads, int f) {
+    chain_release();
+    chain_wait();
+    // one warp a (token, head)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + warp;
+    const int t = (int)(unit / n_heads), head = (int)(unit % n_heads);
+    const float d = den[unit];
+    const float* nr = num + (size_t)unit * f;
+    float ss = 0.f;
+    for (int j = lane; j < f; j += 32) {
+        const float o = nr[j] / d;
+        ss = fmaf(o, o, ss);
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)f + eps);
+    for (int j = lane; j < f; j += 32) {
+        const float o = nr[j] / d;
+        const float z = Elem<T>::load(gate + (size_t)t * gate_row + g_off + head * f + j);
+        Elem<T>::store(out + (size_t)unit * f + j,
+                       o * inv * load_as_float(w, head * f + j, w_dtype) / (1.0f + expf(-z)));
+    }
+}
+
+template <typename T, int MAXR>
+int launch_scan(const void* qkvg, int row_w, int q_off, int k_off, int v_off, const float* gates,
+                const void* bi, const void* bf, int b_dtype, float cap, const int* cu_q,
+                const int* state_slot, float* state, long long slot_stride, int n_requests,
+                int n_heads, int e, int f, int fc, int n_groups, float* num, float* den,
+                cudaStream_t stream) {
+    const int eg_count = SCAN_THREADS / fc;
+    const size_t smem = (size_t)(3 * e + fc + eg_count * fc + 33) * sizeof(float);
+    if (smem > 200 * 1024) return MLS_ERR_UNSUPPORTED;
+    if (smem > 48 * 1024) {
+        const int rc = (int)cudaFuncSetAttribute(mlstm_scan_kernel<T, MAXR>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 (int)smem);
+        if (rc) return rc;
+    }
+    MLS_LAUNCH((mlstm_scan_kernel<T, MAXR>), dim3(n_groups, n_heads, n_requests),
+               dim3(SCAN_THREADS), smem, stream, (const T*)qkvg, row_w, q_off, k_off, v_off, gates,
+               bi, bf, b_dtype, cap, cu_q, state_slot, state, slot_stride, n_heads, e, f, fc,
+               n_groups, num, den);
+    return launch_status();
+}
+
+template <typename T>
+int pick_scan(int maxr, const void* qkvg, int row_w, int q_off, int k_off, int v_off,
+              const float* gates, const void* bi, const void* bf, int b_dtype, float cap,
+              const int* cu_q, const int* state_slot, float* state, long long slot_stride,
+              int n_requests, int n_heads, int e, int f, int fc, int n_groups, float* num,
+              float* den, cudaStream_t stream) {
+#define MLS_SCAN(R)                                                                            \
+    return launch_scan<T, R>(qkvg, row_w, q_off, k_off, v_off, gates, bi, bf, b_dtype, cap,    \
+                             cu_q, state_slot, state, slot_stride, n_requests, n_heads, e, f,  \
+                             fc, n_groups, num, den, stream)
+    if (maxr <= 8) MLS_SCAN(8);
+    if (maxr <= 16) MLS_SCAN(16);
+    if (maxr <= 32) MLS_SCAN(32);
+    if (maxr <= 64) MLS_SCAN(64);
+#undef MLS_SCAN
+    return MLS_ERR_UNSUPPORTED;
+}
+}  // namespace
+
+// Columns of C a CTA owns for heads of (e, f): as many as leave a thread at most 64 rows,
+// at most 64 and at most f.  The state row of a head is e*f + e + ceil(f / columns) floats.
+MLS_API int mls_mlstm_columns(int e, int f) {
+    int fc = f < 64 ? f : 64;
+    while (fc > 1 && (e + (SCAN_THREADS / fc) - 1) / (SCAN_THREADS / fc) > 64) fc = (fc + 1) / 2;
+    return fc;
+}
+
+MLS_API int mls_mlstm_scan(const void* qkvg, int dtype, int row_w, int q_off, int k_off, int v_off,
+                           const float* gates, const void* bias_i, const void* bias_f, int b_dtype,
+                           float cap, const int* cu_q, const int* state_slot, float* state,
+                           long long slot_stride, int n_requests, int n_heads, int e, int f,
+                           float* num, float* den, cudaStream_t stream) {
+    if (n_requests <= 0) return 0;
+    if (e <= 0 || f <= 0 || n_heads <= 0 || n_heads > 65535 || n_requests > 65535)
+        return MLS_ERR_UNSUPPORTED;
+    const int fc = mls_mlstm_columns(e, f);
+    const int eg_count = SCAN_THREADS / fc;
+    const int maxr = (e + eg_count - 1) / eg_count;
+    const int n_groups = (f + fc - 1) / fc;
+    if (dtype == MLS_BF16)
+        return pick_scan<__nv_bfloat16>(maxr, qkvg, row_w, q_off, k_off, v_off, gates, bias_i,
+                                        bias_f, b_dtype, cap, cu_q, state_slot, state, slot_stride,
+                                        n_requests, n_heads, e, f, fc, n_groups, num, den, stream);
+    return pick_scan<float>(maxr, qkvg, row_w, q_off, k_off, v_off, gates, bias_i, bias_f, b_dtype,
+                            cap, cu_q, state_slot, state, slot_stride, n_requests, n_heads, e, f,
+                            fc, n_groups, num, den, stream);
+}
+
+MLS_API int mls_mlstm_finish(const float* num, const float* den, const void* gate, int gate_row,
+                             int g_off, const void* w, int w_dtype, float eps, void* out, int dtype,
+                             int n_tokens, int n_heads, int f, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const long long units = (long long)n_tokens * n_heads;
+    // units is a multiple of nothing in particular: the last block's spare warps would read
+    // past the end, so blocks of one warp when it does not divide
+    const int warps = units % 4 == 0 ? 4 : 1;
+    const int blocks = (int)(units / warps);
+    if (dtype == MLS_BF16)
+        MLS_LAUNCH((mlstm_finish_kernel<__nv_bfloat16>), dim3(blocks), dim3(32 * warps), 0, stream,
+                   num, den, (const __nv_bfloat16*)gate, gate_row, g_off, w, w_dtype, eps,
+                   (__nv_bfloat16*)out, n_heads, f);
+    else
+        MLS_LAUNCH((mlstm_finish_kernel<float>), dim3(blocks), dim3(32 * warps), 0, stream, num, den,
+                   (const float*)gate, gate_row, g_off, w, w_dtype, eps, (float*)out, n_heads, f);
+    return launch_status();
+}

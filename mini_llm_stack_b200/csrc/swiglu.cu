@@ -58,7 +58,45 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     Elem<T>::store(out + t * (size_t)inter + i,
                    silu_mul(Elem<T>::load(row + i), Elem<T>::load(row + inter + i)));
 }
+
+// The gated product with another gate: g' = min(g, limit), u' = clamp(u, -limit, limit),
+// out = g' * sigmoid(alpha * g') * (u' + 1).  (limit <= 0: no clamping.)
+__device__ __forceinline__ float clamped_glu(float g, float u, float alpha, float limit) {
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    return (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+}
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
+                                   float alpha, float limit) {
+    chain_release();
+    chain_wait();
+    const size_t t = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= inter) return;
+    const T* row = gu + t * 2 * (size_t)inter;
+    Elem<T>::store(out + t * (size_t)inter + i,
+                   clamped_glu(Elem<T>::load(row + i), Elem<T>::load(row + inter + i), alpha,
+                               limit));
+}
 }  // namespace
+
+// gu: [T, 2*I], a row holds [gate | up]; out[t, i] = clamped_glu(gate, up).
+MLS_API int mls_clamped_glu(const void* gu, void* out, int dtype, int n_tokens, int inter,
+                            float alpha, float limit, cudaStream_t stream) {
+    if (n_tokens <= 0 || inter <= 0) return 0;
+    const int threads = 256;
+    dim3 grid((inter + threads - 1) / threads, n_tokens);
+    if (dtype == MLS_BF16)
+        MLS_LAUNCH((clamped_glu_kernel<__nv_bfloat16>), dim3(grid), dim3(threads), 0, stream,
+                   (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, alpha, limit);
+    else
+        MLS_LAUNCH((clamped_glu_kernel<float>), dim3(grid), dim3(threads), 0, stream,
+                   (const float*)gu, (float*)out, inter, alpha, limit);
+    return launch_status();
+}
 
 MLS_API int mls_swiglu(const void* gu, void* out, int dtype, int n_tokens, int inter,
                        cudaStream_t stream) {

@@ -29,7 +29,7 @@ import sys
 from pathlib import Path
 
 PAGE_SIZE = 16          # divides 64, so the rounding of --max-tokens is kept
-MAX_LIVE = 8            # state slots; a trace holds up to four live requests
+MAX_LIVE = 4            # state slots: a trace holds up to four live requests, so slots are used again
 
 
 def main(argv=None) -> int:

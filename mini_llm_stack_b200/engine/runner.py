@@ -114,13 +114,21 @@ class ModelRunner:
         self._capture_stream = None
         self.runtime = model.runtime
         cfg = model.config
+        specs = model.cache_specs()
+        # a request whose every token keeps a page can never be longer than the pool; a model
+        # without positions of its own would otherwise ask for block tables of its nominal
+        # length (pages a window gives back let a request outgrow the pool)
+        max_len = cfg.max_seq_len
+        paged = [s for s in specs if hasattr(s, "window")]
+        if paged and all(s.window is None for s in paged):
+            max_len = min(max_len, num_blocks * block_size)
+        self.max_seq_len = max_len
         self.cache = CacheManager(
-            model.cache_specs(), num_blocks=num_blocks, block_size=block_size,
-            max_requests=max_requests, max_seq_len=cfg.max_seq_len,
+            specs, num_blocks=num_blocks, block_size=block_size,
+            max_requests=max_requests, max_seq_len=max_len,
             device=self.runtime.device, kv_dtype=self.runtime.act_dtype)
         self.handles = self.cache.handles()
-        self.builder = BatchBuilder(self.cache, self.runtime.device, cfg.vocab_size,
-                                    cfg.max_seq_len)
+        self.builder = BatchBuilder(self.cache, self.runtime.device, cfg.vocab_size, max_len)
         self.steps = 0
 
     def reserve(self, entries: list) -> None:

@@ -134,6 +134,8 @@ class Ops:
                                      [_P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
                                       _I, _F, _I, _LL, _P])
         self._swiglu = _decl(core, "mls_swiglu", [_P, _P, _I, _I, _I, _P])
+        self._clamped_glu = _decl(core, "mls_clamped_glu", [_P, _P, _I, _I, _I, _F, _F, _P])
+        self._part_libs: dict = {}               # kernels of parts only some models have
         self._sample = _decl(core, "mls_sample", [_P, _P, _P, _P, _I, _I, _P, _P])
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._attention_libs: dict = {}
@@ -620,6 +622,236 @@ class Ops:
         self.launches += 1
         _check(self._swiglu(_ptr(gu), _ptr(out), _code(out.dtype), t, inter, self._stream()),
                "swiglu")
+
+    # ------------------------------------------- parts only some architectures have
+    def _part_lib(self, name: str):
+        """The kernels of a kind of part, built and loaded when a model first needs them."""
+        fns = self._part_libs.get(name)
+        if fns is not None:
+            return fns
+        lib = self._load(name)
+        if name == "layernorm":
+            fns = {"add_layernorm": _decl(lib, "mls_add_layernorm",
+                                          [_P, _P, _I, _I, _LL, _P, _P, _I, _P, _I, _F, _P, _I,
+                                           _I, _I, _P, _P]),
+                   "residual_add": _decl(lib, "mls_residual_add", [_P, _P, _P, _I, _I, _I, _P])}
+        elif name == "latent":
+            fns = {"norm_store": _decl(lib, "mls_latent_norm_store",
+                                       [_P, _I, _I, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _I,
+                                        _LL, _P, _P]),
+                   "headwise": _decl(lib, "mls_headwise_linear",
+                                     [_P, _LL, _LL, _P, _P, _LL, _LL, _I, _I, _I, _I, _I, _P])}
+        elif name == "mlstm":
+            fns = {"columns": _decl(lib, "mls_mlstm_columns", [_I, _I]),
+                   "scan": _decl(lib, "mls_mlstm_scan",
+                                 [_P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _F, _P, _P, _P, _LL,
+                                  _I, _I, _I, _I, _P, _P, _P]),
+                   "finish": _decl(lib, "mls_mlstm_finish",
+                                   [_P, _P, _P, _I, _I, _P, _I, _F, _P, _I, _I, _I, _I, _P])}
+        elif name == "experts":
+            fns = {"tile_rows": _decl(lib, "mls_expert_tile_rows", []),
+                   "topk": _decl(lib, "mls_route_topk", [_P, _I, _I, _I, _I, _P, _P, _P]),
+                   "sort": _decl(lib, "mls_route_sort", [_P, _I, _I, _P, _P, _P, _P, _I, _P, _P]),
+                   "glu": _decl(lib, "mls_expert_glu",
+                                [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P]),
+                   "down": _decl(lib, "mls_expert_down",
+                                 [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P]),
+                   "combine": _decl(lib, "mls_expert_combine",
+                                    [_P, _I, _P, _I, _P, _I, _I, _I, _P])}
+        else:
+            raise KernelError(f"no kernels of a part called {name!r}")
+        self._part_libs[name] = fns
+        return fns
+
+    def require_part(self, name: str) -> None:
+        """Build and load a part's kernels now (at bind time, not in the first step)."""
+        self._part_lib(name)
+
+    def add_layernorm(self, x, delta, weight, eps: float, h, rows=None, n_rows: int = 0,
+                      more_rows=None, more_vec=None) -> None:
+        """``x += delta + more_rows + more_vec`` (each optional; ``delta`` a tensor or
+        ``SplitParts``), ``h = layernorm(x) * weight`` (no bias).  With ``rows`` only
+        those rows are read and ``x`` stays as it is."""
+        t, d = x.shape
+        n_out = t if rows is None else n_rows
+        _need(x.dtype == torch.float32 and x.is_contiguous(), "add_layernorm: x must be float32")
+        _need(h.shape == (n_out, d) and h.is_contiguous(), "add_layernorm: bad output")
+        _need(weight.shape == (d,), "add_layernorm: bad weight")
+        _need(more_rows is None or (more_rows.shape == (t, d) and more_rows.dtype == torch.float32
+                                    and more_rows.is_contiguous()), "add_layernorm: bad rows")
+        _need(more_vec is None or (more_vec.shape == (d,) and more_vec.is_contiguous()),
+              "add_layernorm: bad vector")
+        _need(rows is None or (rows.dtype == torch.int32 and rows.numel() >= n_rows),
+              "add_layernorm: bad row indices")
+        dp, dcode, parts, stride = self._delta_args(delta, t, d, "add_layernorm")
+        self.launches += 1
+        _check(self._part_lib("layernorm")["add_layernorm"](
+            _ptr(x), dp, dcode, parts, stride, _ptr(more_rows), _ptr(more_vec),
+            _code(more_vec.dtype) if more_vec is not None else 0, _ptr(weight),
+            _code(weight.dtype), float(eps), _ptr(h), _code(h.dtype), n_out, d, _ptr(rows),
+            self._stream()), "add_layernorm")
+        if isinstance(delta, SplitParts):
+            delta.release()
+
+    def residual_add(self, x, more_rows=None, more_vec=None) -> None:
+        """``x += more_rows + more_vec`` on the float32 residual stream."""
+        t, d = x.shape
+        _need(x.dtype == torch.float32 and x.is_contiguous(), "residual_add: x must be float32")
+        _need(more_rows is None or (more_rows.shape == (t, d) and more_rows.dtype == torch.float32
+                                    and more_rows.is_contiguous()), "residual_add: bad rows")
+        _need(more_vec is None or (more_vec.shape == (d,) and more_vec.is_contiguous()),
+              "residual_add: bad vector")
+        self.launches += 1
+        _check(self._part_lib("layernorm")["residual_add"](
+            _ptr(x), _ptr(more_rows), _ptr(more_vec),
+            _code(more_vec.dtype) if more_vec is not None else 0, t, d, self._stream()),
+            "residual_add")
+
+    def clamped_glu(self, gu, out, alpha: float, limit: float) -> None:
+        """``out = g' * sigmoid(alpha * g') * (u' + 1)`` with ``g' = min(g, limit)`` and
+        ``u' = clamp(u, -limit, limit)``; a row of ``gu`` holds [gate | up]."""
+        t, inter = out.shape
+        _need(gu.shape == (t, 2 * inter) and gu.dtype == out.dtype, "clamped_glu: shapes")
+        _need(gu.is_contiguous() and out.is_contiguous(), "clamped_glu: layout")
+        self.launches += 1
+        _check(self._clamped_glu(_ptr(gu), _ptr(out), _code(out.dtype), t, inter, float(alpha),
+                                 float(limit), self._stream()), "clamped_glu")
+
+    def latent_norm_store(self, down, q_rank: int, rank: int, wq, wkv, eps: float, cq, cache,
+                          step) -> None:
+        """From the down projections ``down [T, q_rank + rank]`` (float32): the normalised
+        query latent into ``cq`` and the normalised key/value latent into the pool at the
+        step's slots (rows zero-padded to the pool's width)."""
+        g = step.groups[cache.group]
+        t = step.n_tokens
+        pool = cache.k_pool
+        _need(down.shape == (t, q_rank + rank) and down.dtype == torch.float32
+              and down.is_contiguous(), "latent_norm_store: bad projections")
+        _need(pool.is_contiguous() and pool.shape[0] == 1 and pool.shape[3] >= rank,
+              "latent_norm_store: bad pool")
+        _need(q_rank == 0 or (cq.shape == (t, q_rank) and cq.dtype == pool.dtype
+                              and cq.is_contiguous()), "latent_norm_store: bad query latent")
+        _need(wkv.shape == (rank,) and (q_rank == 0 or (wq.shape == (q_rank,)
+                                                        and wq.dtype == wkv.dtype)),
+              "latent_norm_store: bad norm weights")
+        self.launches += 1
+        _check(self._part_lib("latent")["norm_store"](
+            _ptr(down), t, q_rank, rank, pool.shape[3], _ptr(wq), _ptr(wkv), _code(wkv.dtype),
+            float(eps), _ptr(cq), _code(pool.dtype), _ptr(g.slot_map), _ptr(pool), g.block_size,
+            pool.shape[1] * pool.shape[2], _ptr(self.status), self._stream()),
+            "latent_norm_store")
+
+    def headwise_linear(self, src, src_width: int, w, dst, dst_width: int, n_tokens: int) -> None:
+        """``dst[t, h, :N] = w[h] @ src[t, h, :K]`` for ``w [H, N, K]``: rows of ``src`` /
+        ``dst`` are ``src.shape[1]`` / ``dst.shape[1]`` wide and hold the heads
+        ``src_width`` / ``dst_width`` apart."""
+        heads, n, k = w.shape
+        _need(w.is_contiguous() and src.is_contiguous() and dst.is_contiguous()
+              and src.dtype == w.dtype == dst.dtype, "headwise_linear: operands")
+        _need(src.shape[0] >= n_tokens and dst.shape[0] >= n_tokens
+              and src.shape[1] >= (heads - 1) * src_width + k
+              and dst.shape[1] >= (heads - 1) * dst_width + n, "headwise_linear: shapes")
+        self.launches += 1
+        _check(self._part_lib("latent")["headwise"](
+            _ptr(src), src.shape[1], src_width, _ptr(w), _ptr(dst), dst.shape[1], dst_width,
+            _code(w.dtype), n_tokens, heads, n, k, self._stream()), "headwise_linear")
+
+    def mlstm_state_width(self, e: int, f: int) -> int:
+        """Floats of one head's state: the memory [e, f], the normaliser [e] and one
+        stabiliser per group of columns a CTA owns."""
+        fc = int(self._part_lib("mlstm")["columns"](e, f))
+        return e * f + e + (f + fc - 1) // fc
+
+    def mlstm_scan(self, qkvg, offsets: tuple, gates, bias_i, bias_f, cap: float, step, state,
+                   n_heads: int, e: int, f: int, num, den) -> None:
+        """Walk every request's tokens through the matrix memory.  ``qkvg [T, *]`` holds
+        q, k and v at the column ``offsets``; ``gates [T, 2H]`` float32 the input and
+        forget pre-activations; ``num [T, H*f]``, ``den [T, H]`` float32 come out."""
+        t = step.n_tokens
+        width = n_heads * self.mlstm_state_width(e, f)
+        _need(state.dtype == torch.float32 and state.is_contiguous()
+              and state[0].numel() == width, "mlstm_scan: bad state")
+        _need(gates.shape == (t, 2 * n_heads) and gates.dtype == torch.float32
+              and gates.is_contiguous(), "mlstm_scan: bad gates")
+        _need(qkvg.is_contiguous() and num.shape == (t, n_heads * f) and den.shape == (t, n_heads)
+              and num.dtype == den.dtype == torch.float32, "mlstm_scan: bad buffers")
+        _need(bias_i.shape == (n_heads,) and bias_f.dtype == bias_i.dtype, "mlstm_scan: bad biases")
+        q_off, k_off, v_off = offsets
+        self.launches += 1
+        _check(self._part_lib("mlstm")["scan"](
+            _ptr(qkvg), _code(qkvg.dtype), qkvg.shape[1], q_off, k_off, v_off, _ptr(gates),
+            _ptr(bias_i), _ptr(bias_f), _code(bias_i.dtype), float(cap), _ptr(step.cu_q),
+            _ptr(step.state_slot), _ptr(state), width, step.n_requests, n_heads, e, f, _ptr(num),
+            _ptr(den), self._stream()), "mlstm_scan")
+
+    def mlstm_finish(self, num, den, qkvg, g_off: int, weight, eps: float, out, n_heads: int,
+                     f: int) -> None:
+        """``out = unit_rms_per_head(num / den) * weight * sigmoid(gate)``."""
+        t = num.shape[0]
+        _need(out.shape == (t, n_heads * f) and out.is_contiguous() and out.dtype == qkvg.dtype,
+              "mlstm_finish: bad output")
+        _need(weight.shape == (n_heads * f,), "mlstm_finish: bad weight")
+        self.launches += 1
+        _check(self._part_lib("mlstm")["finish"](
+            _ptr(num), _ptr(den), _ptr(qkvg), qkvg.shape[1], g_off, _ptr(weight),
+            _code(weight.dtype), float(eps), _ptr(out), _code(out.dtype), t, n_heads, f,
+            self._stream()), "mlstm_finish")
+
+    def route(self, logits, top: int, renorm: bool, work: dict) -> None:
+        """Choose and sort: from float32 router ``logits [T, E]`` the ``top`` experts a
+        token with sigmoid scores as weights, then the (token, choice) slots ordered by
+        expert.  ``work`` holds the int32 / float32 arrays (``expert_work``)."""
+        t, n_experts = logits.shape
+        _need(logits.dtype == torch.float32 and logits.is_contiguous(), "route: logits")
+        fns = self._part_lib("experts")
+        self.launches += 2
+        _check(fns["topk"](_ptr(logits), t, n_experts, top, 1 if renorm else 0,
+                           _ptr(work["idx"]), _ptr(work["weight"]), self._stream()), "route_topk")
+        _check(fns["sort"](_ptr(work["idx"]), t * top, n_experts, _ptr(work["order"]),
+                           _ptr(work["offsets"]), _ptr(work["tile_expert"]),
+                           _ptr(work["tile_row0"]), work["max_tiles"], _ptr(work["cursor"]),
+                           self._stream()), "route_sort")
+
+    def expert_max_tiles(self, n_slots: int, n_experts: int) -> int:
+        rows = int(self._part_lib("experts")["tile_rows"]())
+        return (n_slots + rows - 1) // rows + n_experts
+
+    def expert_glu(self, h, w_gate_up, y, work: dict, top: int, scale_in: bool) -> None:
+        """``y[p] = silu(Wg[e] a) * (Wu[e] a)`` for the sorted slots; ``w_gate_up [E, 2F, K]``."""
+        n_experts, f2, k = w_gate_up.shape
+        _need(h.dtype == w_gate_up.dtype == y.dtype and h.is_contiguous() and y.is_contiguous()
+              and w_gate_up.is_contiguous() and h.shape[1] == k and y.shape[1] == f2 // 2,
+              "expert_glu: operands")
+        self.launches += 1
+        _check(self._part_lib("experts")["glu"](
+            _ptr(h), _ptr(w_gate_up), _ptr(y), _code(h.dtype), _ptr(work["order"]),
+            _ptr(work["offsets"]), _ptr(work["tile_expert"]), _ptr(work["tile_row0"]),
+            work["max_tiles"], _ptr(work["weight"]), top, 1 if scale_in else 0, f2 // 2, k,
+            self._stream()), "expert_glu")
+
+    def expert_down(self, y, w_down, per_slot, work: dict, top: int, scale_out: bool) -> None:
+        """``per_slot[slot] = Wd[e] y[p]`` (float32); ``w_down [E, D, F]``."""
+        n_experts, d, f = w_down.shape
+        _need(y.dtype == w_down.dtype and y.is_contiguous() and w_down.is_contiguous()
+              and y.shape[1] == f and per_slot.dtype == torch.float32 and per_slot.is_contiguous()
+              and per_slot.shape[1] == d, "expert_down: operands")
+        self.launches += 1
+        _check(self._part_lib("experts")["down"](
+            _ptr(y), _ptr(w_down), _ptr(per_slot), _code(y.dtype), _ptr(work["order"]),
+            _ptr(work["offsets"]), _ptr(work["tile_expert"]), _ptr(work["tile_row0"]),
+            work["max_tiles"], _ptr(work["weight"]), top, 1 if scale_out else 0, d, f,
+            self._stream()), "expert_down")
+
+    def expert_combine(self, per_slot, top: int, shared, delta) -> None:
+        """``delta[t] = sum_j per_slot[t * top + j] + shared[t]``."""
+        t, d = delta.shape
+        _need(per_slot.shape == (t * top, d) and delta.is_contiguous(), "expert_combine: shapes")
+        _need(shared is None or (shared.shape == (t, d) and shared.is_contiguous()),
+              "expert_combine: bad shared addend")
+        self.launches += 1
+        _check(self._part_lib("experts")["combine"](
+            _ptr(per_slot), top, _ptr(shared), _code(shared.dtype) if shared is not None else 0,
+            _ptr(delta), _code(delta.dtype), t, d, self._stream()), "expert_combine")
 
     def sample(self, logits, temperature, uniform, out) -> None:
         """Tokens for float32 ``logits [n, V]``; rows with temperature <= 0 (or

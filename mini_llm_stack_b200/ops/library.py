@@ -41,6 +41,11 @@ MODULES = {
     "attention": ["attention_mma.cu", "attention_tc.cu"],
     "gemm": ["gemm_tcgen05.cu"],
     "argmax_static": ["argmax_static.cu"],
+    # parts only some architectures have: built when a model with such a part is loaded
+    "layernorm": ["layernorm.cu"],
+    "latent": ["latent.cu"],
+    "mlstm": ["mlstm.cu"],
+    "experts": ["experts.cu"],
 }
 
 
@@ -52,6 +57,7 @@ def all_modules(head_sizes=()) -> list:
     if (CSRC / "gemm_tcgen05.cu").is_file():
         out.append(("gemm", {}))
     out.append(("argmax_static", {}))
+    out += [(name, {}) for name in ("layernorm", "latent", "mlstm", "experts")]
     return out
 
 

@@ -65,6 +65,41 @@ def context_splits(tiles: list, n_kv: int, slots: int = 296, cluster_splits: int
     return best
 
 
+def plan_paged_attention(step: StepContext, facts: dict, n_heads: int, n_kv_heads: int,
+                         head_dim: int):
+    """A step's ``AttentionPlan`` for heads of this shape (None where the kernel in use
+    needs none), shared through ``step.attn_tiles`` by the mixers of the same shape.
+
+    Requests whose (token, head) rows of one kv head fit ``small_rows`` go to the
+    context-split kernel, their context cut so that all SMs have work; the others
+    are cut into tiles of rows."""
+    f = facts
+    if not f["tensor_cores"]:
+        return None
+    group = n_heads // n_kv_heads
+    key = ("gqa", group, n_kv_heads, head_dim)
+    plan = step.attn_tiles.get(key)
+    if plan is None:
+        small = [q * group <= f["small_rows"] for q in step.q_lens]
+        big = [q * group for q, s in zip(step.q_lens, small) if not s]
+        n_small = sum(small)
+        n_split = 1
+        if n_small:
+            keys = f.get("split_keys", 64)
+            tiles = [-(-c // keys) for c, s in zip(step.ctx_lens, small) if s]
+            n_split = context_splits(tiles, n_kv_heads, f["split_slots"],
+                                     f.get("cluster_splits", 0),
+                                     longest=-(-step.max_ctx_len // keys),
+                                     cluster_slots=f.get("cluster_slots", 0))
+        plan = AttentionPlan(
+            n_tiles=sum(-(-r // f["tile_rows"]) for r in big),
+            n_tiles_tc=sum(-(-r // f["tc_rows"]) for r in big),
+            n_tiles_tc_wide=sum(-(-r // (2 * f["tc_rows"])) for r in big),
+            any_small=n_small > 0, n_split=n_split)
+        step.attn_tiles[key] = plan
+    return plan
+
+
 class GroupedQueryAttention(Mixer):
     def __init__(self, d_model: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  scale: float, position, window=None):
@@ -116,31 +151,8 @@ class GroupedQueryAttention(Mixer):
         context-split kernel, their context cut so that all SMs have work; the others
         are cut into tiles of rows.  Mixers with the same shape of heads share the
         plan of a step."""
-        f = self._facts
-        if not f["tensor_cores"]:
-            return None
-        group = self.n_heads // self.n_kv_heads
-        key = ("gqa", group, self.n_kv_heads, self.head_dim)
-        plan = step.attn_tiles.get(key)
-        if plan is None:
-            small = [q * group <= f["small_rows"] for q in step.q_lens]
-            big = [q * group for q, s in zip(step.q_lens, small) if not s]
-            n_small = sum(small)
-            n_split = 1
-            if n_small:
-                keys = f.get("split_keys", 64)
-                tiles = [-(-c // keys) for c, s in zip(step.ctx_lens, small) if s]
-                n_split = context_splits(tiles, self.n_kv_heads, f["split_slots"],
-                                         f.get("cluster_splits", 0),
-                                         longest=-(-step.max_ctx_len // keys),
-                                         cluster_slots=f.get("cluster_slots", 0))
-            plan = AttentionPlan(
-                n_tiles=sum(-(-r // f["tile_rows"]) for r in big),
-                n_tiles_tc=sum(-(-r // f["tc_rows"]) for r in big),
-                n_tiles_tc_wide=sum(-(-r // (2 * f["tc_rows"])) for r in big),
-                any_small=n_small > 0, n_split=n_split)
-            step.attn_tiles[key] = plan
-        return plan
+        return plan_paged_attention(step, self._facts, self.n_heads, self.n_kv_heads,
+                                    self.head_dim)
 
     def decode_graph_key(self, step: StepContext) -> tuple:
         """What, besides the number of requests, fixes this mixer's launches in a step

@@ -53,10 +53,15 @@ class TensorSpec:
 # ----------------------------------------------------------------------------
 @dataclass(frozen=True)
 class PagedKV:
-    """Keys and values of every token (or of the last ``window`` tokens)."""
+    """Keys and values of every token (or of the last ``window`` tokens).
+
+    ``shared_kv``: one pool serves as keys and as values (a mixer that attends over a
+    single cached vector a token, such as a latent); the handle's ``k_pool`` and
+    ``v_pool`` are then the same tensor."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    shared_kv: bool = False
 
 
 @dataclass(frozen=True)
@@ -141,6 +146,24 @@ class ResidualStream:
     def __init__(self, x: torch.Tensor):
         self.x = x                   # [T, d_model] float32
         self.pending = None
+        self.more_rows = None        # float32 [T, d_model], added row by row by the next norm
+        self.more_vec = None         # [d_model], added to every row by the next norm
+
+    def push_more(self, rows=None, vec=None) -> None:
+        """Addends besides the pending delta (a second stream, a vector for every row);
+        the next norm adds them in the pass in which it adds the delta."""
+        if (rows is not None and self.more_rows is not None) or \
+                (vec is not None and self.more_vec is not None):
+            raise RuntimeError("such an addend is already waiting on the residual stream")
+        if rows is not None:
+            self.more_rows = rows
+        if vec is not None:
+            self.more_vec = vec
+
+    def take_more(self):
+        out = (self.more_rows, self.more_vec)
+        self.more_rows = self.more_vec = None
+        return out
 
     def push(self, delta) -> None:
         if self.pending is not None:

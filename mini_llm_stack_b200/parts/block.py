@@ -10,6 +10,25 @@ from __future__ import annotations
 from .base import CacheHandle, Part, ResidualStream, StepContext
 
 
+def join_name(prefix: str, name: str) -> str:
+    """``prefix.name``; an empty ``name`` is the prefix itself (a part whose one tensor
+    carries the part's own name)."""
+    if not name:
+        return prefix
+    return f"{prefix}.{name}" if prefix else name
+
+
+def under_prefix(tensors: dict, prefix: str) -> dict:
+    """The tensors of ``prefix`` under their local names (``prefix`` itself becomes "")."""
+    out = {}
+    for n, t in tensors.items():
+        if n == prefix:
+            out[""] = t
+        elif n.startswith(prefix + "."):
+            out[n[len(prefix) + 1:]] = t
+    return out
+
+
 class PreNormBlock(Part):
     def __init__(self, mixer_norm, mixer, ffn_norm, ffn,
                  names=("attn_norm", "attn", "mlp_norm", "mlp")):
@@ -18,22 +37,22 @@ class PreNormBlock(Part):
         self.names = tuple(names)
 
     def _named_parts(self):
-        return list(zip(self.names,
-                        (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)))
+        """(prefix, part) of the parts there are; a block without a feed-forward
+        (``ffn`` None) has no second norm either."""
+        return [(n, p) for n, p in zip(self.names, (self.mixer_norm, self.mixer,
+                                                    self.ffn_norm, self.ffn)) if p is not None]
 
     def tensor_specs(self) -> dict:
         out = {}
         for prefix, part in self._named_parts():
             for n, s in part.tensor_specs().items():
-                out[f"{prefix}.{n}"] = s
+                out[join_name(prefix, n)] = s
         return out
 
     def bind(self, tensors: dict, runtime) -> None:
         self.runtime = runtime
         for prefix, part in self._named_parts():
-            own = {n[len(prefix) + 1:]: t for n, t in tensors.items()
-                   if n.startswith(prefix + ".")}
-            part.bind(own, runtime)
+            part.bind(under_prefix(tensors, prefix), runtime)
 
     def cache_spec(self):
         return self.mixer.cache_spec()
@@ -53,5 +72,7 @@ class PreNormBlock(Part):
                 cache: CacheHandle) -> None:
         h = self.mixer_norm.forward(stream)
         stream.push(self.mixer.forward(h, step, cache))
+        if self.ffn is None:
+            return
         h = self.ffn_norm.forward(stream)
         stream.push(self.ffn.forward(h, step))

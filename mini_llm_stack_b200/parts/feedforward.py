@@ -1,4 +1,4 @@
-"""Dense SwiGLU feed-forward.
+"""Feed-forwards: dense SwiGLU, a clamped gated unit, and routed experts.
 
 Reference (train/model.py:127-135): ``w_down(silu(w_gate x) * (w_up x))`` with
 ``silu(z) = z * sigmoid(z)``, no biases.  Gate and up share one projection
@@ -16,20 +16,21 @@ from .base import FeedForward, StepContext, TensorSpec
 class SwiGLUFeedForward(FeedForward):
     decode_capturable = prompt_capturable = True   # forward only launches kernels on the current stream
 
-    def __init__(self, d_model: int, intermediate_size: int):
+    def __init__(self, d_model: int, intermediate_size: int,
+                 names=("w_gate.weight", "w_up.weight", "w_down.weight")):
         self.d_model, self.intermediate_size = int(d_model), int(intermediate_size)
+        self.names = tuple(names)             # local names of the gate, up and down matrices
         self.w_gate_up = self.w_down = None
 
     def tensor_specs(self) -> dict:
         d, i = self.d_model, self.intermediate_size
-        return {
-            "w_gate.weight": TensorSpec((i, d)),
-            "w_up.weight": TensorSpec((i, d)),
-            "w_down.weight": TensorSpec((d, i)),
-        }
+        g, u, dn = self.names
+        return {g: TensorSpec((i, d)), u: TensorSpec((i, d)), dn: TensorSpec((d, i))}
 
     def bind(self, tensors: dict, runtime) -> None:
         self.runtime = runtime
+        tensors = {"w_gate.weight": tensors[self.names[0]], "w_up.weight": tensors[self.names[1]],
+                   "w_down.weight": tensors[self.names[2]]}
         parts = [tensors["w_gate.weight"], tensors["w_up.weight"]]
         if parts[0].dtype != parts[1].dtype:
             parts = [p.float() for p in parts]
@@ -57,3 +58,118 @@ class SwiGLUFeedForward(FeedForward):
             rt.ops.swiglu(gu, act)
         delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)
         return rt.ops.linear_parts(act, self.w_down, delta)
+
+
+class ClampedGLUFeedForward(FeedForward):
+    """``W_down (g' * sigmoid(alpha * g') * (u' + 1))`` with ``g' = min(W_gate h, limit)``
+    and ``u' = clamp(W_up h, -limit, limit)``; no biases.  The activation runs in
+    float32 on the projection's output."""
+
+    decode_capturable = prompt_capturable = True
+
+    def __init__(self, d_model: int, intermediate_size: int, limit: float, alpha: float = 1.702,
+                 names=("gate", "up", "down")):
+        self.d_model, self.intermediate_size = int(d_model), int(intermediate_size)
+        self.limit, self.alpha = float(limit), float(alpha)
+        self.names = tuple(names)
+
+    def tensor_specs(self) -> dict:
+        d, i = self.d_model, self.intermediate_size
+        g, u, dn = self.names
+        return {g: TensorSpec((i, d)), u: TensorSpec((i, d)), dn: TensorSpec((d, i))}
+
+    def bind(self, tensors: dict, runtime) -> None:
+        self.runtime = runtime
+        g, u, dn = self.names
+        self.w_gate_up = runtime.ops.prepare_weight(torch.cat([tensors[g], tensors[u]], dim=0))
+        self.w_down = runtime.ops.prepare_weight(tensors[dn])
+
+    def forward(self, h, step: StepContext):
+        rt = self.runtime
+        t, i = h.shape[0], self.intermediate_size
+        gu = rt.buffer("gate_up", (t, 2 * i), rt.act_dtype)
+        rt.ops.linear(h, self.w_gate_up, gu)
+        act = rt.buffer("ffn_act", (t, i), rt.act_dtype)
+        rt.ops.clamped_glu(gu, act, self.alpha, self.limit)
+        delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)
+        return rt.ops.linear_parts(act, self.w_down, delta)
+
+
+class RoutedExperts(FeedForward):
+    """A mixture of small SwiGLU experts with a sigmoid router.
+
+    Router logits ``z = W_r h`` and scores ``s = sigmoid(z)`` in float32; a token takes
+    its ``top`` experts with the largest scores (lowest index on a tie) and weighs them
+    by the scores themselves (``renormalise``: divided by their sum).  ``weigh`` says
+    where a weight multiplies: "input" (the expert sees ``w * h``) or "output".  A
+    ``shared`` feed-forward, if any, runs for every token and is added.  Tensors:
+    ``router`` [E, d] and ``e<i>.gate / up / down`` for every expert; the shared
+    part's under ``shared``."""
+
+    decode_capturable = prompt_capturable = True
+
+    def __init__(self, d_model: int, n_experts: int, top: int, expert_size: int, shared=None,
+                 weigh: str = "input", renormalise: bool = False):
+        if weigh not in ("input", "output"):
+            raise ValueError(f"weigh must be 'input' or 'output', not {weigh!r}")
+        if not 0 < int(top) <= int(n_experts):
+            raise ValueError("top must lie in 1..n_experts")
+        self.d_model, self.n_experts, self.top = int(d_model), int(n_experts), int(top)
+        self.expert_size, self.shared = int(expert_size), shared
+        self.weigh, self.renormalise = weigh, bool(renormalise)
+
+    def tensor_specs(self) -> dict:
+        d, f = self.d_model, self.expert_size
+        out = {"router": TensorSpec((self.n_experts, d))}
+        for i in range(self.n_experts):
+            out[f"e{i}.gate"] = TensorSpec((f, d))
+            out[f"e{i}.up"] = TensorSpec((f, d))
+            out[f"e{i}.down"] = TensorSpec((d, f))
+        if self.shared is not None:
+            out.update({f"shared.{n}": s for n, s in self.shared.tensor_specs().items()})
+        return out
+
+    def bind(self, tensors: dict, runtime) -> None:
+        self.runtime = runtime
+        n = self.n_experts
+        self.w_router = tensors["router"].float().contiguous()       # scores are float32
+        self.w_gate_up = torch.stack([torch.cat([tensors[f"e{i}.gate"], tensors[f"e{i}.up"]], 0)
+                                      for i in range(n)]).contiguous()
+        self.w_down = torch.stack([tensors[f"e{i}.down"] for i in range(n)]).contiguous()
+        if self.shared is not None:
+            self.shared.bind({k[len("shared."):]: v for k, v in tensors.items()
+                              if k.startswith("shared.")}, runtime)
+        runtime.ops.require_part("experts")
+
+    def _work(self, t: int) -> dict:
+        rt, n_slots = self.runtime, t * self.top
+        tiles = rt.ops.expert_max_tiles(n_slots, self.n_experts)
+        i32 = torch.int32
+        return {"idx": rt.buffer("route_idx", (n_slots,), i32),
+                "weight": rt.buffer("route_weight", (n_slots,), torch.float32),
+                "order": rt.buffer("route_order", (n_slots,), i32),
+                "offsets": rt.buffer("route_offsets", (self.n_experts + 1,), i32),
+                "cursor": rt.buffer("route_cursor", (self.n_experts,), i32),
+                "tile_expert": rt.buffer("route_tile_expert", (tiles,), i32),
+                "tile_row0": rt.buffer("route_tile_row0", (tiles,), i32),
+                "max_tiles": tiles}
+
+    def forward(self, h, step: StepContext):
+        rt, ops = self.runtime, self.runtime.ops
+        t = h.shape[0]
+        logits = rt.buffer("route_logits", (t, self.n_experts), torch.float32)
+        ops.linear(h, self.w_router, logits)
+        work = self._work(t)
+        ops.route(logits, self.top, self.renormalise, work)
+        y = rt.buffer("expert_act", (t * self.top, self.expert_size), rt.act_dtype)
+        ops.expert_glu(h, self.w_gate_up, y, work, self.top, self.weigh == "input")
+        per_slot = rt.buffer("expert_out", (t * self.top, self.d_model), torch.float32)
+        ops.expert_down(y, self.w_down, per_slot, work, self.top, self.weigh == "output")
+        shared = None
+        if self.shared is not None:
+            shared = self.shared.forward(h, step)
+            if not isinstance(shared, torch.Tensor):
+                shared = shared.float()              # a product left as its K-parts
+        delta = rt.buffer("routed_delta", (t, self.d_model), rt.act_dtype)
+        ops.expert_combine(per_slot, self.top, shared, delta)
+        return delta

@@ -13,6 +13,7 @@ from dataclasses import dataclass
 from typing import Optional
 
 from .base import CacheHandle, Part, ResidualStream, StepContext, TensorSpec
+from .block import join_name, under_prefix
 
 
 @dataclass(frozen=True)
@@ -20,6 +21,35 @@ class LayerCall:
     layer: int                    # index into ComposedModel.blocks
     cache_slot: Optional[int]     # index into ComposedModel.cache_specs()
     writes: bool = True           # False: reads a slot an earlier call filled
+    entry: Optional[tuple] = None  # (index into ComposedModel.entries, number of the pass):
+    #                                what is added to the stream right before this call
+
+
+class PassEntry(Part):
+    """What enters the residual stream at the start of a pass over a run of layers that
+    is repeated: before every pass but the first the embedding's output (the stream as
+    it was before the first layer), and before every pass the pass's own row of a
+    learned table ``[passes, d_model]``.  Both are handed to the stream as waiting
+    addends, so the first norm of the pass adds them while it reads the rows anyway."""
+
+    decode_capturable = prompt_capturable = True
+
+    def __init__(self, d_model: int, passes: int, tensor_name: str = "step",
+                 add_embedding: bool = True):
+        self.d_model, self.passes = int(d_model), int(passes)
+        self.tensor_name, self.add_embedding = tensor_name, add_embedding
+        self.table = None
+
+    def tensor_specs(self) -> dict:
+        return {self.tensor_name: TensorSpec((self.passes, self.d_model), kind="matrix")}
+
+    def bind(self, tensors: dict, runtime) -> None:
+        self.runtime = runtime
+        self.table = tensors[self.tensor_name].contiguous()
+
+    def forward(self, stream: ResidualStream, number: int, embedded) -> None:
+        stream.push_more(rows=embedded if (self.add_embedding and number > 0) else None,
+                         vec=self.table[number])
 
 
 class TokenEmbedding(Part):
@@ -27,20 +57,21 @@ class TokenEmbedding(Part):
 
     decode_capturable = prompt_capturable = True
 
-    def __init__(self, vocab_size: int, d_model: int):
+    def __init__(self, vocab_size: int, d_model: int, tensor_name: str = "weight"):
         self.vocab_size, self.d_model = int(vocab_size), int(d_model)
+        self.tensor_name = tensor_name
         self.weight = None
 
     def tensor_specs(self) -> dict:
-        return {"weight": TensorSpec((self.vocab_size, self.d_model))}
+        return {self.tensor_name: TensorSpec((self.vocab_size, self.d_model))}
 
     def bind(self, tensors: dict, runtime) -> None:
         self.runtime = runtime
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.tensor_name].contiguous()
 
-    def forward(self, step: StepContext):
+    def forward(self, step: StepContext, buffer: str = "residual"):
         rt = self.runtime
-        x = rt.buffer("residual", (step.n_tokens, self.d_model), rt.residual_dtype)
+        x = rt.buffer(buffer, (step.n_tokens, self.d_model), rt.residual_dtype)
         rt.ops.embed(step.token_ids, self.weight, x, self.vocab_size)
         return x
 
@@ -77,8 +108,14 @@ class ComposedModel:
 
     def __init__(self, config, embedding: TokenEmbedding, blocks: list,
                  calls: list, final_norm, head: OutputHead,
-                 names=("embed", "blocks", "final_norm", "lm_head"), aliases=None):
+                 names=("embed", "blocks", "final_norm", "lm_head"), aliases=None,
+                 block_prefix=None, entries=()):
+        """``names``: prefixes of the embedding's, the blocks', the final norm's and the
+        head's tensors; ``block_prefix(i)`` overrides ``"<blocks>.<i>"``.  ``entries``:
+        ``[(prefix, PassEntry)]`` that calls refer to by ``LayerCall.entry``."""
         self.config = config
+        self._block_prefix = block_prefix or (lambda i: f"{names[1]}.{i}")
+        self.entries = list(entries)
         self._aliases = aliases          # callable: tensor name -> other names a file may use
         self.embedding, self.blocks, self.calls = embedding, list(blocks), list(calls)
         self.final_norm, self.head = final_norm, head
@@ -99,12 +136,14 @@ class ComposedModel:
     # ------------------------------------------------------------------ tensors
     def tensor_specs(self) -> dict:
         e, b, f, h = self.names
-        out = {f"{e}.{n}": s for n, s in self.embedding.tensor_specs().items()}
+        out = {join_name(e, n): s for n, s in self.embedding.tensor_specs().items()}
+        for prefix, part in self.entries:
+            out.update({join_name(prefix, n): s for n, s in part.tensor_specs().items()})
         for i, blk in enumerate(self.blocks):
             for n, s in blk.tensor_specs().items():
-                out[f"{b}.{i}.{n}"] = s
-        out.update({f"{f}.{n}": s for n, s in self.final_norm.tensor_specs().items()})
-        out.update({f"{h}.{n}": s for n, s in self.head.tensor_specs().items()})
+                out[join_name(self._block_prefix(i), n)] = s
+        out.update({join_name(f, n): s for n, s in self.final_norm.tensor_specs().items()})
+        out.update({join_name(h, n): s for n, s in self.head.tensor_specs().items()})
         return out
 
     def name_aliases(self) -> dict:
@@ -118,8 +157,8 @@ class ComposedModel:
     def tied_names(self) -> dict:
         """Names a file may hold although the model takes them from another."""
         e, _, _, h = self.names
-        if self.head.tied_to is not None:
-            return {f"{h}.weight": f"{e}.weight"}
+        if self.head.tied_to is not None and h:
+            return {f"{h}.weight": join_name(e, self.embedding.tensor_name)}
         return {}
 
     def bind(self, tensors: dict, runtime) -> None:
@@ -127,12 +166,13 @@ class ComposedModel:
         e, b, f, h = self.names
 
         def sub(prefix):
-            return {n[len(prefix) + 1:]: t for n, t in tensors.items()
-                    if n.startswith(prefix + ".")}
+            return under_prefix(tensors, prefix) if prefix else {}
 
         self.embedding.bind(sub(e), runtime)
+        for prefix, part in self.entries:
+            part.bind(sub(prefix), runtime)
         for i, blk in enumerate(self.blocks):
-            blk.bind(sub(f"{b}.{i}"), runtime)
+            blk.bind(sub(self._block_prefix(i)), runtime)
         self.final_norm.bind(sub(f), runtime)
         self.head.bind(sub(h), runtime)
 
@@ -142,7 +182,8 @@ class ComposedModel:
 
     # ------------------------------------------------------------------- graphs
     def _all_parts(self) -> list:
-        return [self.embedding, *self.blocks, self.final_norm, self.head]
+        return [self.embedding, *(p for _, p in self.entries), *self.blocks, self.final_norm,
+                self.head]
 
     @property
     def decode_capturable(self) -> bool:
@@ -169,8 +210,15 @@ class ComposedModel:
         """Run the step's tokens; float32 logits [n_out, vocab] at ``out_rows``."""
         self.runtime.ops.begin_step(step.n_tokens)
         stream = ResidualStream(self.embedding.forward(step))
+        embedded = None
+        if any(c.entry is not None and c.entry[1] > 0 for c in self.calls):
+            # the stream moves on in place: a pass that starts over from the embedding's
+            # output reads a second copy of it
+            embedded = self.embedding.forward(step, buffer="embedded")
         none = CacheHandle()
         for call in self.calls:
+            if call.entry is not None:
+                self.entries[call.entry[0]][1].forward(stream, call.entry[1], embedded)
             handle = none
             if call.cache_slot is not None:
                 handle = handles[call.cache_slot]

@@ -1,4 +1,4 @@
-"""RMS norm with a learned weight.
+"""Norms: RMS norm with a learned weight, and layer norm with a weight and no bias.
 
 Reference formula (train/model.py:29-33): ``xf = x.float()``;
 ``y = xf * rsqrt(mean(xf**2, -1) + eps)``; ``out = (y * w.float()).to(x.dtype)``.
@@ -35,6 +35,11 @@ class RMSNorm(Norm):
         as it was.
         """
         rt = self.runtime
+        more_rows, more_vec = stream.take_more()
+        if more_rows is not None or more_vec is not None:
+            if rows is not None:
+                raise RuntimeError("addends beside the delta cannot be settled for picked rows")
+            rt.ops.residual_add(stream.x, more_rows, more_vec)
         delta = stream.take_pending()
         if rows is None:
             t = stream.x.shape[0]
@@ -44,4 +49,37 @@ class RMSNorm(Norm):
             h = rt.buffer("normed_rows", (n_rows, self.dim), rt.act_dtype)
             rt.ops.gather_add_rmsnorm(stream.x, delta, rows, n_rows, self.weight,
                                       self.eps, h)
+        return h
+
+
+class LayerNorm(Norm):
+    """``(x - mean) / sqrt(var + eps) * w`` with the biased variance and no bias, in
+    float32 with one rounding.  Adds the stream's pending delta and its other waiting
+    addends (``ResidualStream.push_more``) in the same pass.  ``tensor_name`` is the
+    local name of the weight ("" = the part's own prefix)."""
+
+    decode_capturable = prompt_capturable = True
+
+    def __init__(self, dim: int, eps: float, tensor_name: str = "weight"):
+        self.dim, self.eps, self.tensor_name = int(dim), float(eps), tensor_name
+        self.weight = None
+
+    def tensor_specs(self) -> dict:
+        return {self.tensor_name: TensorSpec((self.dim,), kind="vector", init="ones")}
+
+    def bind(self, tensors: dict, runtime) -> None:
+        self.runtime = runtime
+        self.weight = tensors[self.tensor_name].contiguous()
+        runtime.ops.require_part("layernorm")
+
+    def forward(self, stream: ResidualStream, rows=None, n_rows: int = 0):
+        rt = self.runtime
+        more_rows, more_vec = stream.take_more()
+        delta = stream.take_pending()
+        if rows is None:
+            h = rt.buffer("normed", (stream.x.shape[0], self.dim), rt.act_dtype)
+        else:
+            h = rt.buffer("normed_rows", (n_rows, self.dim), rt.act_dtype)
+        rt.ops.add_layernorm(stream.x, delta, self.weight, self.eps, h, rows=rows, n_rows=n_rows,
+                             more_rows=more_rows, more_vec=more_vec)
         return h
