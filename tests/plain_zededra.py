@@ -3,14 +3,23 @@
 Written from the design's equations with torch tensor algebra only; it shares
 no code with the engine.  Everything runs in the dtype of the weights it is
 given (float64 for an oracle, float32 otherwise); ``tokens`` is one sequence.
+``rnd`` (identity by default) is applied to every activation a 16-bit engine
+would store (projections, mixer and feed-forward outputs, normed rows): with
+``to_bf16`` the function shows how far rounding alone moves a result.
 
 Notation: d = model width, H = heads, e = query/key size of a head, f = value
 size of a head, r = latent size, eps = the model's norm epsilon.
 """
 
-import math
-
 import torch
+
+
+def ident(t):
+    return t
+
+
+def to_bf16(t):
+    return t.to(torch.bfloat16).to(t.dtype)
 
 
 # --------------------------------------------------------------------------- norms
@@ -27,23 +36,23 @@ def plain_unit_rms(x, eps):
 
 
 # --------------------------------------------------------------- latent attention
-def plain_latent_attention(h, w, p, m, eps):
+def plain_latent_attention(h, w, p, m, eps, rnd=ident):
     """Causal softmax attention whose keys and values are read off one shared
     latent a token: c = unit_rms(W_dkv h) * g_kv; k_h = W_uk[h] c; v_h = W_uv[h] c;
     queries through a latent of their own.  No positions enter."""
     S = h.shape[0]
     H, e, f = m["heads"], m["dim"], m["vdim"]
-    cq = plain_unit_rms(h @ w[f"{p}.dq"].T, eps) * w[f"{p}.dq.norm"]
-    q = (cq @ w[f"{p}.uq"].T).view(S, H, e)
-    c = plain_unit_rms(h @ w[f"{p}.dkv"].T, eps) * w[f"{p}.dkv.norm"]
-    k = (c @ w[f"{p}.uk"].T).view(S, H, e)
-    v = (c @ w[f"{p}.uv"].T).view(S, H, f)
+    cq = rnd(plain_unit_rms(h @ w[f"{p}.dq"].T, eps) * w[f"{p}.dq.norm"])
+    q = rnd(cq @ w[f"{p}.uq"].T).view(S, H, e)
+    c = rnd(plain_unit_rms(h @ w[f"{p}.dkv"].T, eps) * w[f"{p}.dkv.norm"])
+    k = rnd(c @ w[f"{p}.uk"].T).view(S, H, e)
+    v = rnd(c @ w[f"{p}.uv"].T).view(S, H, f)
     s = torch.einsum("ihe,jhe->hij", q, k) * m["scale"]
     hidden = torch.triu(torch.ones(S, S, dtype=torch.bool), diagonal=1)
     s = s.masked_fill(hidden, float("-inf"))
     a = torch.softmax(s, dim=-1)
-    o = torch.einsum("hij,jhf->ihf", a, v).reshape(S, H * f)
-    return o @ w[f"{p}.o"].T, c
+    o = rnd(torch.einsum("hij,jhf->ihf", a, v).reshape(S, H * f))
+    return rnd(o @ w[f"{p}.o"].T), c
 
 
 # -------------------------------------------------------------------------- mLSTM
@@ -51,7 +60,7 @@ def plain_soft_cap(z, cap):
     return cap * torch.tanh(z / cap)
 
 
-def plain_mlstm(h, w, p, m, eps, state=None):
+def plain_mlstm(h, w, p, m, eps, state=None, rnd=ident):
     """Matrix memory with exponential gates, token by token.
 
     log gates: i = softcap(W_i h + b_i), f = logsigmoid(softcap(W_f h + b_f));
@@ -63,9 +72,9 @@ def plain_mlstm(h, w, p, m, eps, state=None):
     S = h.shape[0]
     H, e, f = m["heads"], m["dim"], m["vdim"]
     cap = m["gate_cap"]
-    q = (h @ w[f"{p}.q"].T).view(S, H, e) * e ** -0.5
-    k = (h @ w[f"{p}.k"].T).view(S, H, e)
-    v = (h @ w[f"{p}.v"].T).view(S, H, f)
+    q = rnd(h @ w[f"{p}.q"].T).view(S, H, e) * e ** -0.5
+    k = rnd(h @ w[f"{p}.k"].T).view(S, H, e)
+    v = rnd(h @ w[f"{p}.v"].T).view(S, H, f)
     ig = plain_soft_cap(h @ w[f"{p}.i"].T + w[f"{p}.i.b"], cap)
     fg = torch.nn.functional.logsigmoid(plain_soft_cap(h @ w[f"{p}.f"].T + w[f"{p}.f.b"], cap))
     if state is None:
@@ -87,21 +96,21 @@ def plain_mlstm(h, w, p, m, eps, state=None):
         rows.append(num / den[:, None])
     o = torch.stack(rows)                                   # [S, H, f]
     o = plain_unit_rms(o, eps).reshape(S, H * f) * w[f"{p}.norm"]
-    o = o * torch.sigmoid(h @ w[f"{p}.g"].T)
-    return o @ w[f"{p}.o"].T, (C, n, mx)
+    o = rnd(o * torch.sigmoid(rnd(h @ w[f"{p}.g"].T)))
+    return rnd(o @ w[f"{p}.o"].T), (C, n, mx)
 
 
 # ------------------------------------------------------------------ feed-forwards
-def plain_clamped_glu(h, w, p, limit):
+def plain_clamped_glu(h, w, p, limit, rnd=ident):
     """g = min(W_g h, L); u = clamp(W_u h, -L, L); W_d (g sigmoid(1.702 g) (u + 1))."""
-    g = torch.clamp(h @ w[f"{p}.gate"].T, max=limit)
-    u = torch.clamp(h @ w[f"{p}.up"].T, -limit, limit)
-    return (g * torch.sigmoid(1.702 * g) * (u + 1)) @ w[f"{p}.down"].T
+    g = torch.clamp(rnd(h @ w[f"{p}.gate"].T), max=limit)
+    u = torch.clamp(rnd(h @ w[f"{p}.up"].T), -limit, limit)
+    return rnd(rnd(g * torch.sigmoid(1.702 * g) * (u + 1)) @ w[f"{p}.down"].T)
 
 
-def plain_silu_glu(h, w, p):
+def plain_silu_glu(h, w, p, rnd=ident):
     g = h @ w[f"{p}.gate"].T
-    return (g * torch.sigmoid(g) * (h @ w[f"{p}.up"].T)) @ w[f"{p}.down"].T
+    return rnd(g * torch.sigmoid(g) * (h @ w[f"{p}.up"].T)) @ w[f"{p}.down"].T
 
 
 def plain_route(h, w_router, top):
@@ -112,7 +121,7 @@ def plain_route(h, w_router, top):
     return order.indices[:, :top], order.values[:, :top]
 
 
-def plain_routed_experts(h, w, p, mlp):
+def plain_routed_experts(h, w, p, mlp, rnd=ident):
     """sum over the chosen experts of expert(weight * h), plus the shared expert."""
     top = mlp["router"]["top"]
     idx, val = plain_route(h, w[f"{p}.router"], top)
@@ -120,16 +129,16 @@ def plain_routed_experts(h, w, p, mlp):
     for t in range(h.shape[0]):
         for j in range(top):
             ex = int(idx[t, j])
-            out[t] += plain_silu_glu((val[t, j].to(h.dtype) * h[t])[None], w, f"{p}.e{ex}")[0]
+            out[t] += plain_silu_glu((val[t, j].to(h.dtype) * h[t])[None], w, f"{p}.e{ex}", rnd)[0]
     if mlp.get("shared"):
-        out = out + plain_silu_glu(h, w, f"{p}.shared")
-    return out
+        out = out + rnd(plain_silu_glu(h, w, f"{p}.shared", rnd))
+    return rnd(out)
 
 
-def plain_feedforward(h, w, p, mlp):
+def plain_feedforward(h, w, p, mlp, rnd=ident):
     if mlp["kind"] == "dense":
-        return plain_clamped_glu(h, w, p, mlp["limit"])
-    return plain_routed_experts(h, w, p, mlp)
+        return plain_clamped_glu(h, w, p, mlp["limit"], rnd)
+    return plain_routed_experts(h, w, p, mlp, rnd)
 
 
 # -------------------------------------------------------------------------- model
@@ -147,7 +156,7 @@ def layer_runs(cfg):
     return runs
 
 
-def plain_zededra(w, cfg, tokens, trace=None):
+def plain_zededra(w, cfg, tokens, trace=None, rnd=ident):
     """Logits [S, vocab] of one whole sequence; ``trace`` (a list) receives the
     residual stream after every layer run."""
     eps = cfg["norm"]["eps"]
@@ -159,17 +168,17 @@ def plain_zededra(w, cfg, tokens, trace=None):
             if t > 0:
                 x = x + x0
             x = x + w["loop.step"][t]
-        h = plain_layernorm(x, w[f"l{i}.norm1"], eps)
+        h = rnd(plain_layernorm(x, w[f"l{i}.norm1"], eps))
         if L["type"] == "mlstm":
-            y, _ = plain_mlstm(h, w, f"l{i}.mix", L["mixer"], eps)
+            y, _ = plain_mlstm(h, w, f"l{i}.mix", L["mixer"], eps, rnd=rnd)
         elif L["type"] == "latent_attention":
-            y, _ = plain_latent_attention(h, w, f"l{i}.mix", L["mixer"], eps)
+            y, _ = plain_latent_attention(h, w, f"l{i}.mix", L["mixer"], eps, rnd)
         else:
             raise ValueError(L["type"])
         x = x + y
         if L.get("mlp"):
-            h = plain_layernorm(x, w[f"l{i}.norm2"], eps)
-            x = x + plain_feedforward(h, w, f"l{i}.mlp", L["mlp"])
+            h = rnd(plain_layernorm(x, w[f"l{i}.norm2"], eps))
+            x = x + plain_feedforward(h, w, f"l{i}.mlp", L["mlp"], rnd)
         if trace is not None:
             trace.append(x)
-    return plain_layernorm(x, w["final.norm"], eps) @ w["embed"].T
+    return rnd(plain_layernorm(x, w["final.norm"], eps)) @ w["embed"].T
