@@ -369,10 +369,25 @@ def main() -> int:
     ap.add_argument("--workload", default="decode", choices=["decode", "mixed_1b", "poisson_7b"],
                     help="decode: the contract's line; the others serve a request mix through "
                          "the scheduler and print their own line")
+    ap.add_argument("--design", default=None, choices=["zededra"],
+                    help="instead of the contract's line: layers of this design at sizes that "
+                         "resemble a real model's, beside the dense decoder at equal size "
+                         "(prefill and decode tokens/s and the time of every kind of kernel)")
+    ap.add_argument("--size", default=None, choices=["1b", "8b"],
+                    help="with --design: only this size (default: all)")
     args = ap.parse_args()
 
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design:
+        import importlib.util
+        spec = importlib.util.spec_from_file_location("design_bench",
+                                                      ROOT / "baseline" / "design_bench.py")
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        sys.path.insert(0, str(ROOT))
+        pk, pk_src = peaks()
+        return mod.main(args, pk, pk_src)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2

@@ -20,7 +20,7 @@
 #include "common.cuh"
 
 namespace {
-constexpr int BM = 32, BN = 64, BK = 16, TM = 2, TN = 4;   // 256 threads
+constexpr int BM = 32, BN = 64, BK = 32, TM = 2, TN = 4;   // 256 threads
 
 __global__ void route_topk_kernel(const float* __restrict__ logits, int n_tokens, int n_experts,
                                   int top, int renorm, int* __restrict__ idx,
@@ -103,10 +103,64 @@ route_sort_kernel(const int* __restrict__ idx, int n_slots, int n_experts,
         order[atomicAdd(&cursor[idx[s]], 1)] = s;
 }
 
-// GLU: A row = h[slot / top] (* weight[slot] if scale_in), W = [gate rows | up rows] of
+// 16 bytes of a row as floats: eight bfloat16 or four float32.
+template <typename T> struct Vec;
+template <> struct Vec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float* out) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+    }
+};
+template <> struct Vec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* out) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            out[2 * e] = f.x;
+            out[2 * e + 1] = f.y;
+        }
+    }
+};
+
+// Fill tile[k][row] (k < BK, row < ROWS) from rows of K-contiguous values: row r comes from
+// src(r) (nullptr: zeros), scaled by scale(r).  16-byte loads where K allows them.
+template <typename T, int ROWS, int PAD, typename Src>
+__device__ __forceinline__ void fill_tile(float (*tile)[ROWS + PAD], int k0, int K, bool vec_ok,
+                                          Src src) {
+    constexpr int V = Vec<T>::N;
+    if (vec_ok) {
+        for (int u = threadIdx.x; u < ROWS * (BK / V); u += 256) {
+            const int r = u / (BK / V), kv = (u - r * (BK / V)) * V;
+            float scale = 1.f;
+            const T* p = src(r, scale);
+            float v[V];
+            if (p && k0 + kv < K) {
+                Vec<T>::load(p + k0 + kv, v);
+            } else {
+#pragma unroll
+                for (int e = 0; e < V; ++e) v[e] = 0.f;
+            }
+#pragma unroll
+            for (int e = 0; e < V; ++e) tile[kv + e][r] = v[e] * scale;
+        }
+    } else {
+        for (int u = threadIdx.x; u < ROWS * BK; u += 256) {
+            const int r = u / BK, k = u - r * BK;
+            float scale = 1.f;
+            const T* p = src(r, scale);
+            tile[k][r] = (p && k0 + k < K) ? Elem<T>::load(p + k0 + k) * scale : 0.f;
+        }
+    }
+}
+
+// GLU: A row = h[slot / top] (* weight[slot] if scale), W = [gate rows | up rows] of
 // expert e ([2F, K]), out y[p, n] = silu(gate) * up in T.
 // !GLU: A row = y[p], W = Wd[e] ([N, K]), out per_slot[slot, n] float32 (* weight[slot]
-// if scale_out).
+// if scale).  A thread owns rows ty*TM.. and the columns tx, tx + 16, tx + 32, tx + 48.
 template <typename T, bool GLU>
 __global__ void __launch_bounds__(256)
 expert_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __restrict__ out,
@@ -117,17 +171,19 @@ expert_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __res
     chain_wait();
     const int e = tile_expert[blockIdx.y];
     if (e < 0) return;
-    __shared__ float As[BK][BM + 4];
-    __shared__ float Ws[BK][BN + 4];
-    __shared__ float Us[GLU ? BK : 1][BN + 4];
+    __shared__ float As[BK][BM + 1];
+    __shared__ float Ws[BK][BN + 1];
+    __shared__ float Us[GLU ? BK : 1][BN + 1];
     __shared__ int slot_s[BM];
     const int tid = threadIdx.x;
     const int p0 = tile_row0[blockIdx.y], p_end = offsets[e + 1];
     const int n0 = blockIdx.x * BN;
-    const int tx = tid % (BN / TN), ty = tid / (BN / TN);      // 16 x 16
+    const int tx = tid % 16, ty = tid / 16;                     // 16 x 16
     if (tid < BM) slot_s[tid] = p0 + tid < p_end ? order[p0 + tid] : -1;
     __syncthreads();
     const T* We = W + (size_t)e * (GLU ? 2 : 1) * N * K;
+    const bool vec_ok = K % Vec<T>::N == 0 &&
+                        (reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) % 16 == 0;
     float acc[TM][TN], acu[GLU ? TM : 1][TN];
 #pragma unroll
     for (int i = 0; i < TM; ++i)
@@ -136,33 +192,23 @@ expert_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __res
             acc[i][j] = 0.f;
             if (GLU) acu[i][j] = 0.f;
         }
-    // A tile: 32 rows x 16 k = 512 values, two a thread; W tile: 64 rows x 16 k, four a thread
-    const int arow = tid >> 3, ak = (tid & 7) * 2;
-    const int wrow = tid >> 2, wk = (tid & 3) * 4;
-    const int aslot = slot_s[arow];
-    const T* arow_p = nullptr;
-    float ascale = 1.f;
-    if (aslot >= 0) {
-        if (GLU) {
-            arow_p = A + (size_t)(aslot / top) * K;
-            if (scale) ascale = weight[aslot];
-        } else {
-            arow_p = A + (size_t)(p0 + arow) * K;
-        }
-    }
     for (int k0 = 0; k0 < K; k0 += BK) {
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
-            const int k = k0 + ak + x;
-            As[ak + x][arow] = (arow_p && k < K) ? Elem<T>::load(arow_p + k) * ascale : 0.f;
-        }
-#pragma unroll
-        for (int x = 0; x < 4; ++x) {
-            const int k = k0 + wk + x, n = n0 + wrow;
-            const bool ok = n < N && k < K;
-            Ws[wk + x][wrow] = ok ? Elem<T>::load(We + (size_t)n * K + k) : 0.f;
-            if (GLU) Us[wk + x][wrow] = ok ? Elem<T>::load(We + (size_t)(N + n) * K + k) : 0.f;
-        }
+        fill_tile<T, BM, 1>(As, k0, K, vec_ok, [&](int r, float& sc) -> const T* {
+            const int slot = slot_s[r];
+            if (slot < 0) return nullptr;
+            if (GLU) {
+                if (scale) sc = weight[slot];
+                return A + (size_t)(slot / top) * K;
+            }
+            return A + (size_t)(p0 + r) * K;
+        });
+        fill_tile<T, BN, 1>(Ws, k0, K, vec_ok, [&](int r, float&) -> const T* {
+            return n0 + r < N ? We + (size_t)(n0 + r) * K : nullptr;
+        });
+        if (GLU)
+            fill_tile<T, BN, 1>(Us, k0, K, vec_ok, [&](int r, float&) -> const T* {
+                return n0 + r < N ? We + (size_t)(N + n0 + r) * K : nullptr;
+            });
         __syncthreads();
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
@@ -171,8 +217,8 @@ expert_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __res
             for (int i = 0; i < TM; ++i) a[i] = As[kk][ty * TM + i];
 #pragma unroll
             for (int j = 0; j < TN; ++j) {
-                w[j] = Ws[kk][tx * TN + j];
-                if (GLU) u[j] = Us[kk][tx * TN + j];
+                w[j] = Ws[kk][tx + 16 * j];
+                if (GLU) u[j] = Us[kk][tx + 16 * j];
             }
 #pragma unroll
             for (int i = 0; i < TM; ++i)
@@ -191,7 +237,7 @@ expert_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __res
         if (slot < 0) continue;
 #pragma unroll
         for (int j = 0; j < TN; ++j) {
-            const int n = n0 + tx * TN + j;
+            const int n = n0 + tx + 16 * j;
             if (n >= N) continue;
             if (GLU) {
                 const float g = acc[i][j];

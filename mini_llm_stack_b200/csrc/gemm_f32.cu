@@ -62,11 +62,63 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
         }
     }
 }
+
+// Few output columns (a router's or a gate's scores: N <= SKINNY_N): the tile kernel above
+// would leave all but a few SMs idle and walk K in steps of 16 behind two barriers each.
+// Here a block holds SK_ROWS rows of A in shared memory, a warp owns the output columns
+// n = warp, warp + 8, ... and its lanes walk K with a stride of 32; the 32 partial sums are
+// added by a fixed tree.  The order of the additions depends on K alone (never on M or on
+// the row's place in its block), and which kernel runs depends on N alone, so a token's
+// result still does not depend on its batch.
+constexpr int SKINNY_N = 64, SK_ROWS = 8, SK_KC = 1024;
+
+__global__ void __launch_bounds__(256)
+gemm_f32_skinny_kernel(const float* __restrict__ A, const float* __restrict__ W,
+                       float* __restrict__ out, int M, int N, int K) {
+    chain_release();
+    chain_wait();
+    __shared__ float As[SK_ROWS][SK_KC];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * SK_ROWS;
+    for (int n0 = 0; n0 < N; n0 += 8) {
+        const int n = n0 + warp;
+        float acc[SK_ROWS];
+#pragma unroll
+        for (int r = 0; r < SK_ROWS; ++r) acc[r] = 0.f;
+        for (int k0 = 0; k0 < K; k0 += SK_KC) {
+            const int kc = min(SK_KC, K - k0);
+            __syncthreads();
+            for (int i = threadIdx.x; i < SK_ROWS * kc; i += 256) {
+                const int r = i / kc, k = i - r * kc;
+                As[r][k] = m0 + r < M ? A[(size_t)(m0 + r) * K + k0 + k] : 0.f;
+            }
+            __syncthreads();
+            if (n < N) {
+                const float* wr = W + (size_t)n * K + k0;
+                for (int k = lane; k < kc; k += 32) {
+                    const float w = wr[k];
+#pragma unroll
+                    for (int r = 0; r < SK_ROWS; ++r) acc[r] = fmaf(As[r][k], w, acc[r]);
+                }
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < SK_ROWS; ++r) {
+            const float s = warp_sum(acc[r]);
+            if (lane == 0 && n < N && m0 + r < M) out[(size_t)(m0 + r) * N + n] = s;
+        }
+    }
+}
 }  // namespace
 
 MLS_API int mls_gemm_f32(const float* A, const float* W, float* out, int M, int N, int K,
                          cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
+    if (N <= SKINNY_N) {
+        MLS_LAUNCH((gemm_f32_skinny_kernel), dim3((M + SK_ROWS - 1) / SK_ROWS), dim3(256), 0,
+                   stream, A, W, out, M, N, K);
+        return launch_status();
+    }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     MLS_LAUNCH((gemm_f32_kernel), dim3(grid), dim3(256), 0, stream, A, W, out, M, N, K, N);
     return launch_status();

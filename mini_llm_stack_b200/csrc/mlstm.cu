@@ -16,16 +16,22 @@
 //
 // A CTA owns FC columns of one head's C for one request and keeps them in registers:
 // thread (col, eg) holds the rows eg, eg + EG, ... of its column.  Only the CTA of a
-// head's first columns carries n; every CTA carries its own copy of m (the state row
-// of a head is [C (e*f) | n (e) | m (one per column group)]), so no CTA reads what
-// another writes.  All gate arithmetic, the state and the sums are float32; q, k, v and
-// the gate pre-activations come from the projections.  A token's result depends on the
-// tokens before it only through the state, never on the batch or on how the sequence
-// was cut into steps.
+// head's first columns carries n (a thread holds the elements tid, tid + 256, ...); every
+// CTA carries its own copy of m (the state row of a head is
+// [C (e*f) | n (e) | m (one per column group)]), so no CTA reads what another writes.
+// Tokens are taken TB at a time: one pass loads their q, k, v and gates into shared
+// memory, then every thread walks the block token by token: the scalar recurrence of m,
+// its rows of C, the token's partial output; the partial outputs and the partial n . q
+// are added up once a block, in a fixed order.  All gate
+// arithmetic, the state and the sums are float32; q, k, v and the gate pre-activations
+// come from the projections.  A token's result depends on the tokens before it only
+// through the state, never on the batch or on how the sequence was cut into steps.
 #include "common.cuh"
 
 namespace {
 constexpr int SCAN_THREADS = 256;
+constexpr int TB = 8;                       // tokens a pass
+constexpr int MAXN = 4;                     // elements of n a thread holds: e <= 1024
 
 __device__ __forceinline__ float soft_cap(float z, float cap) { return cap * tanhf(z / cap); }
 __device__ __forceinline__ float log_sigmoid(float z) {
@@ -47,15 +53,17 @@ mlstm_scan_kernel(const T* __restrict__ qkvg, int row_w, int q_off, int k_off, i
     const int grp = blockIdx.x, head = blockIdx.y, req = blockIdx.z;
     const int eg_count = SCAN_THREADS / fc;
     const int col = threadIdx.x % fc, eg = threadIdx.x / fc;
-    const bool active = eg < eg_count && grp * fc + col < f;
     const int gcol = grp * fc + col;
+    const bool active = eg < eg_count && gcol < f;
     const bool first = grp == 0;
-    float* q_s = sm;                       // [e]
-    float* k_s = q_s + e;                  // [e]
-    float* n_s = k_s + e;                  // [e]
-    float* v_s = n_s + e;                  // [fc]
-    float* part = v_s + fc;                // [eg_count][fc]
-    float* red = part + eg_count * fc;     // [33]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float* q_s = sm;                           // [TB][e]
+    float* k_s = q_s + TB * e;                 // [TB][e]
+    float* v_s = k_s + TB * e;                 // [TB][fc]
+    float* part = v_s + TB * fc;               // [TB][eg_count][fc]
+    float* gate_s = part + TB * eg_count * fc; // [2][TB]: log input gate, log forget gate
+    float* nq_s = gate_s + 2 * TB;             // [TB][8 warps]
+    float* m_s = nq_s + TB * 8;                // [TB]: the stabiliser after each token
 
     const int t0 = cu_q[req], t1 = cu_q[req + 1];
     float* st = state + (size_t)state_slot[req] * slot_stride +
@@ -66,58 +74,91 @@ mlstm_scan_kernel(const T* __restrict__ qkvg, int row_w, int q_off, int k_off, i
         const int row = eg + r * eg_count;
         C[r] = (active && row < e) ? st[(size_t)row * f + gcol] : 0.f;
     }
-    if (first)
-        for (int i = threadIdx.x; i < e; i += SCAN_THREADS) n_s[i] = st[(size_t)e * f + i];
+    float nreg[MAXN];
+#pragma unroll
+    for (int x = 0; x < MAXN; ++x) {
+        const int i = threadIdx.x + x * SCAN_THREADS;
+        nreg[x] = (first && i < e) ? st[(size_t)e * f + i] : 0.f;
+    }
     float m = st[(size_t)e * f + e + grp];
     const float bi = load_as_float(bias_i, head, b_dtype), bf = load_as_float(bias_f, head, b_dtype);
     const float q_scale = 1.0f / sqrtf((float)e);
-    __syncthreads();
 
-    for (int t = t0; t < t1; ++t) {
-        const T* row = qkvg + (size_t)t * row_w;
-        for (int i = threadIdx.x; i < e; i += SCAN_THREADS) {
-            q_s[i] = Elem<T>::load(row + q_off + head * e + i) * q_scale;
-            k_s[i] = Elem<T>::load(row + k_off + head * e + i);
+    for (int tb = t0; tb < t1; tb += TB) {
+        const int nb = min(TB, t1 - tb);
+        // ---- the block's inputs
+        for (int u = threadIdx.x; u < nb * e; u += SCAN_THREADS) {
+            const int j = u / e, i = u - j * e;
+            const T* row = qkvg + (size_t)(tb + j) * row_w;
+            q_s[j * e + i] = Elem<T>::load(row + q_off + head * e + i) * q_scale;
+            k_s[j * e + i] = Elem<T>::load(row + k_off + head * e + i);
         }
-        for (int i = threadIdx.x; i < fc; i += SCAN_THREADS)
-            v_s[i] = grp * fc + i < f ? Elem<T>::load(row + v_off + head * f + grp * fc + i) : 0.f;
-        const float ig = soft_cap(gates[(size_t)t * 2 * n_heads + head] + bi, cap);
-        const float fg = log_sigmoid(soft_cap(gates[(size_t)t * 2 * n_heads + n_heads + head] + bf, cap));
-        const float m_new = fmaxf(fg + m, ig);
-        const float keep = expf(fg + m - m_new), take = expf(ig - m_new);
-        m = m_new;
+        for (int u = threadIdx.x; u < nb * fc; u += SCAN_THREADS) {
+            const int j = u / fc, c = u - j * fc;
+            v_s[u] = grp * fc + c < f
+                         ? Elem<T>::load(qkvg + (size_t)(tb + j) * row_w + v_off + head * f + grp * fc + c)
+                         : 0.f;
+        }
+        if (threadIdx.x < nb) {
+            const float* gr = gates + (size_t)(tb + threadIdx.x) * 2 * n_heads;
+            gate_s[threadIdx.x] = soft_cap(gr[head] + bi, cap);
+            gate_s[TB + threadIdx.x] = log_sigmoid(soft_cap(gr[n_heads + head] + bf, cap));
+        }
         __syncthreads();
-        float o = 0.f;
-        if (active) {
-            const float tv = take * v_s[col];
+        // ---- token by token: the stabiliser (walked by every thread for itself), C and the
+        // token's partial output, n and the partial n . q
+#pragma unroll 1
+        for (int j = 0; j < nb; ++j) {
+            const float ig = gate_s[j], fg = gate_s[TB + j];
+            const float m_new = fmaxf(fg + m, ig);
+            const float keep = expf(fg + m - m_new), take = expf(ig - m_new);
+            m = m_new;
+            if (threadIdx.x == 0) m_s[j] = m;
+            if (active) {
+                const float tv = take * v_s[j * fc + col];
+                const float* kj = k_s + j * e;
+                const float* qj = q_s + j * e;
+                float o = 0.f;
 #pragma unroll
-            for (int r = 0; r < MAXR; ++r) {
-                const int rr = eg + r * eg_count;
-                if (rr < e) {
-                    C[r] = fmaf(keep, C[r], k_s[rr] * tv);
-                    o = fmaf(C[r], q_s[rr], o);
+                for (int r = 0; r < MAXR; ++r) {
+                    const int rr = eg + r * eg_count;
+                    if (rr < e) {
+                        C[r] = fmaf(keep, C[r], kj[rr] * tv);
+                        o = fmaf(C[r], qj[rr], o);
+                    }
                 }
+                part[(j * eg_count + eg) * fc + col] = o;
             }
-            part[eg * fc + col] = o;
-        }
-        float nq = 0.f;
-        if (first) {
-            for (int i = threadIdx.x; i < e; i += SCAN_THREADS) {
-                const float nn = fmaf(keep, n_s[i], take * k_s[i]);
-                n_s[i] = nn;
-                nq = fmaf(nn, q_s[i], nq);
+            if (first) {
+                float nq = 0.f;
+#pragma unroll
+                for (int x = 0; x < MAXN; ++x) {
+                    const int i = threadIdx.x + x * SCAN_THREADS;
+                    if (i < e) {
+                        nreg[x] = fmaf(keep, nreg[x], take * k_s[j * e + i]);
+                        nq = fmaf(nreg[x], q_s[j * e + i], nq);
+                    }
+                }
+                nq = warp_sum(nq);
+                if (lane == 0) nq_s[j * 8 + warp] = nq;
             }
-            nq = block_sum(nq, red);             // also orders part[] before the reads below
-        } else {
-            __syncthreads();
         }
-        if (eg == 0 && grp * fc + col < f) {
-            float s = 0.f;
-            for (int g2 = 0; g2 < eg_count; ++g2) s += part[g2 * fc + col];
-            num[(size_t)t * n_heads * f + (size_t)head * f + gcol] = s;
+        __syncthreads();
+        // ---- add up: the column groups' partial outputs, the warps' partial n . q
+        for (int u = threadIdx.x; u < nb * fc; u += SCAN_THREADS) {
+            const int j = u / fc, c = u - j * fc;
+            if (grp * fc + c < f) {
+                float s2 = 0.f;
+                for (int g2 = 0; g2 < eg_count; ++g2) s2 += part[(j * eg_count + g2) * fc + c];
+                num[(size_t)(tb + j) * n_heads * f + (size_t)head * f + grp * fc + c] = s2;
+            }
         }
-        if (first && threadIdx.x == 0)
-            den[(size_t)t * n_heads + head] = fmaxf(fabsf(nq), expf(-m)) + 1e-6f;
+        if (first && threadIdx.x < nb) {
+            const int j = threadIdx.x;
+            float nq = 0.f;
+            for (int w2 = 0; w2 < 8; ++w2) nq += nq_s[j * 8 + w2];
+            den[(size_t)(tb + j) * n_heads + head] = fmaxf(fabsf(nq), expf(-m_s[j])) + 1e-6f;
+        }
         __syncthreads();
     }
 #pragma unroll
@@ -125,8 +166,13 @@ mlstm_scan_kernel(const T* __restrict__ qkvg, int row_w, int q_off, int k_off, i
         const int row = eg + r * eg_count;
         if (active && row < e) st[(size_t)row * f + gcol] = C[r];
     }
-    if (first)
-        for (int i = threadIdx.x; i < e; i += SCAN_THREADS) st[(size_t)e * f + i] = n_s[i];
+    if (first) {
+#pragma unroll
+        for (int x = 0; x < MAXN; ++x) {
+            const int i = threadIdx.x + x * SCAN_THREADS;
+            if (i < e) st[(size_t)e * f + i] = nreg[x];
+        }
+    }
     if (threadIdx.x == 0) st[(size_t)e * f + e + grp] = m;
 }
 
@@ -164,7 +210,8 @@ int launch_scan(const void* qkvg, int row_w, int q_off, int k_off, int v_off, co
                 int n_heads, int e, int f, int fc, int n_groups, float* num, float* den,
                 cudaStream_t stream) {
     const int eg_count = SCAN_THREADS / fc;
-    const size_t smem = (size_t)(3 * e + fc + eg_count * fc + 33) * sizeof(float);
+    const size_t smem = (size_t)(2 * TB * e + TB * fc + TB * eg_count * fc + 2 * TB + TB * 8 + TB) *
+                        sizeof(float);
     if (smem > 200 * 1024) return MLS_ERR_UNSUPPORTED;
     if (smem > 48 * 1024) {
         const int rc = (int)cudaFuncSetAttribute(mlstm_scan_kernel<T, MAXR>,
@@ -189,6 +236,7 @@ int pick_scan(int maxr, const void* qkvg, int row_w, int q_off, int k_off, int v
     return launch_scan<T, R>(qkvg, row_w, q_off, k_off, v_off, gates, bi, bf, b_dtype, cap,    \
                              cu_q, state_slot, state, slot_stride, n_requests, n_heads, e, f,  \
                              fc, n_groups, num, den, stream)
+    if (maxr <= 4) MLS_SCAN(4);
     if (maxr <= 8) MLS_SCAN(8);
     if (maxr <= 16) MLS_SCAN(16);
     if (maxr <= 32) MLS_SCAN(32);
@@ -199,9 +247,11 @@ int pick_scan(int maxr, const void* qkvg, int row_w, int q_off, int k_off, int v
 }  // namespace
 
 // Columns of C a CTA owns for heads of (e, f): as many as leave a thread at most 64 rows,
-// at most 64 and at most f.  The state row of a head is e*f + e + ceil(f / columns) floats.
+// at most 32 (a warp then reads one row of k and q at a time, and one prompt makes enough
+// CTAs for the GPU) and at most f.  The state row of a head is e*f + e + ceil(f / columns)
+// floats.
 MLS_API int mls_mlstm_columns(int e, int f) {
-    int fc = f < 64 ? f : 64;
+    int fc = f < 32 ? f : 32;
     while (fc > 1 && (e + (SCAN_THREADS / fc) - 1) / (SCAN_THREADS / fc) > 64) fc = (fc + 1) / 2;
     return fc;
 }
@@ -212,7 +262,8 @@ MLS_API int mls_mlstm_scan(const void* qkvg, int dtype, int row_w, int q_off, in
                            long long slot_stride, int n_requests, int n_heads, int e, int f,
                            float* num, float* den, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
-    if (e <= 0 || f <= 0 || n_heads <= 0 || n_heads > 65535 || n_requests > 65535)
+    if (e <= 0 || e > MAXN * SCAN_THREADS || f <= 0 || n_heads <= 0 || n_heads > 65535 ||
+        n_requests > 65535)
         return MLS_ERR_UNSUPPORTED;
     const int fc = mls_mlstm_columns(e, f);
     const int eg_count = SCAN_THREADS / fc;

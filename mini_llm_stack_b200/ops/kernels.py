@@ -751,6 +751,19 @@ class Ops:
         _need(src.shape[0] >= n_tokens and dst.shape[0] >= n_tokens
               and src.shape[1] >= (heads - 1) * src_width + k
               and dst.shape[1] >= (heads - 1) * dst_width + n, "headwise_linear: shapes")
+        if (w.dtype == torch.bfloat16 and n_tokens > 64 and self.gemm_impl != "tcgen05"
+                and src.shape[1] % 8 == 0 and dst.shape[1] % 8 == 0 and src_width % 8 == 0
+                and dst_width % 8 == 0 and k % 8 == 0 and n % 8 == 0):
+            # many rows: a plain batched product, handed to the library as the plain
+            # products of more than 64 rows are (the heads are the batch)
+            held = self._transposed.get(id(w))
+            if held is None or held[0] is not w:
+                held = self._transposed[id(w)] = (w, w.transpose(1, 2))
+            a = src.as_strided((heads, n_tokens, k), (src_width, src.shape[1], 1))
+            o = dst.as_strided((heads, n_tokens, n), (dst_width, dst.shape[1], 1))
+            self.library_launches += 1
+            torch.bmm(a, held[1], out=o)
+            return
         self.launches += 1
         _check(self._part_lib("latent")["headwise"](
             _ptr(src), src.shape[1], src_width, _ptr(w), _ptr(dst), dst.shape[1], dst_width,

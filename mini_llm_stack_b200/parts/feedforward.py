@@ -106,7 +106,7 @@ class RoutedExperts(FeedForward):
     ``router`` [E, d] and ``e<i>.gate / up / down`` for every expert; the shared
     part's under ``shared``."""
 
-    decode_capturable = prompt_capturable = True
+    decode_capturable = prompt_capturable = True   # routing, sorting and the products stay on the device
 
     def __init__(self, d_model: int, n_experts: int, top: int, expert_size: int, shared=None,
                  weigh: str = "input", renormalise: bool = False):
@@ -161,9 +161,10 @@ class RoutedExperts(FeedForward):
         ops.linear(h, self.w_router, logits)
         work = self._work(t)
         ops.route(logits, self.top, self.renormalise, work)
-        y = rt.buffer("expert_act", (t * self.top, self.expert_size), rt.act_dtype)
+        n_slots = t * self.top
+        y = rt.buffer("expert_act", (n_slots, self.expert_size), rt.act_dtype)
+        per_slot = rt.buffer("expert_out", (n_slots, self.d_model), torch.float32)
         ops.expert_glu(h, self.w_gate_up, y, work, self.top, self.weigh == "input")
-        per_slot = rt.buffer("expert_out", (t * self.top, self.d_model), torch.float32)
         ops.expert_down(y, self.w_down, per_slot, work, self.top, self.weigh == "output")
         shared = None
         if self.shared is not None:
