@@ -45,9 +45,11 @@ def zededra_config(s: dict, kind: str, layers: int, vocab: int = 32000) -> dict:
 
 
 def llama_config(s: dict, layers: int, vocab: int = 32000) -> dict:
-    # one kv head of the latent's size in keys plus values: the same cache bytes a token
+    # kv heads of the latent's size in keys plus values, i.e. the same cache bytes a token (but
+    # at most 16 query heads a kv head, the most the fused decode attention takes)
     return dict(architecture="llama_dense", vocab_size=vocab, d_model=s["width"], n_layers=layers,
-                n_heads=s["heads"], n_kv_heads=max(1, s["kv_rank"] // (2 * s["dim"])),
+                n_heads=s["heads"],
+                n_kv_heads=max(1, s["kv_rank"] // (2 * s["dim"]), s["heads"] // 16),
                 head_dim=s["dim"], intermediate_size=s["ff"], max_seq_len=4096,
                 rope_theta=500000.0, norm_eps=1e-5, tie_embeddings=True, dtype="bfloat16")
 
@@ -56,7 +58,7 @@ _LEAVES = ("embed", "add_rmsnorm", "gather_add_rmsnorm", "add_layernorm", "resid
            "rope_store", "paged_attention", "attention_decode_fused", "swiglu", "clamped_glu",
            "latent_norm_store", "headwise_linear", "mlstm_scan", "mlstm_finish", "route",
            "expert_glu", "expert_down", "expert_combine")
-_PRODUCTS = ("linear", "linear_parts", "linear_swiglu")
+_PRODUCTS = ("linear", "linear_parts", "linear_swiglu", "linear_clamped_glu")
 
 
 class OpTimer:

@@ -13,7 +13,8 @@
 //   scaling), float32.
 // mls_expert_combine: delta[t] = sum_j per_slot[t * top + j] + shared[t], j ascending.
 //
-// The products run on CUDA cores with float32 accumulation over k ascending, one row
+// The products run with float32 accumulation over k ascending (bfloat16 rows of whole
+// 16-byte pieces on the tensor cores, everything else on CUDA cores), one row
 // tile of one expert a CTA; every row is computed by itself, so a token's result does
 // not depend on the batch, on its place in the sorted order or on the other tokens of
 // its expert.
@@ -250,6 +251,136 @@ expert_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __res
     }
 }
 
+// The same products for bfloat16 on the tensor cores (mma.sync m16n8k16, float32
+// accumulators): a CTA takes the same tile of 32 sorted rows x 64 output columns, its eight
+// warps 16 x 16 each; operands go through shared memory in rows of 32 + 8 values, so that
+// the fragment loads (one 32-bit word a lane) meet no bank twice.  Every output element is
+// its own dot product over k ascending in steps of 16, whatever else is in the tile.  With
+// input scaling the row is rounded to bfloat16 once more after the weight is applied.
+constexpr int MK = 32, MKP = MK + 8;
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <bool GLU>
+__global__ void __launch_bounds__(256)
+expert_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
+                  void* __restrict__ out, const int* __restrict__ order,
+                  const int* __restrict__ offsets, const int* __restrict__ tile_expert,
+                  const int* __restrict__ tile_row0, const float* __restrict__ weight, int top,
+                  int scale, int N, int K) {
+    chain_release();
+    chain_wait();
+    const int e = tile_expert[blockIdx.y];
+    if (e < 0) return;
+    __shared__ __align__(16) __nv_bfloat16 As[BM][MKP];
+    __shared__ __align__(16) __nv_bfloat16 Ws[BN][MKP];
+    __shared__ __align__(16) __nv_bfloat16 Us[GLU ? BN : 1][MKP];
+    __shared__ int slot_s[BM];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int p0 = tile_row0[blockIdx.y], p_end = offsets[e + 1];
+    const int n0 = blockIdx.x * BN;
+    if (tid < BM) slot_s[tid] = p0 + tid < p_end ? order[p0 + tid] : -1;
+    __syncthreads();
+    const __nv_bfloat16* We = W + (size_t)e * (GLU ? 2 : 1) * N * K;
+    const int wm = warp >> 2, wn = warp & 3;                  // 2 x 4 warps of 16 x 16
+    const int g = lane >> 2, c = (lane & 3) * 2;
+    float acc[2][4], acu[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = acu[i][j] = 0.f;
+    // who loads what: 16 bytes a thread and tile
+    const int lrow = tid >> 2, lk = (tid & 3) * 8;
+    const __nv_bfloat16* a_src = nullptr;
+    float a_scale = 1.f;
+    if (tid < BM * 4) {
+        const int slot = slot_s[lrow];
+        if (slot >= 0) {
+            if (GLU) {
+                a_src = A + (size_t)(slot / top) * K;
+                if (scale) a_scale = weight[slot];
+            } else {
+                a_src = A + (size_t)(p0 + lrow) * K;
+            }
+        }
+    }
+    const bool w_ok = n0 + lrow < N;
+    const __nv_bfloat16* w_src = We + (size_t)(n0 + lrow) * K;
+    const __nv_bfloat16* u_src = We + (size_t)(N + n0 + lrow) * K;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int k0 = 0; k0 < K; k0 += MK) {
+        const bool k_ok = k0 + lk < K;
+        if (tid < BM * 4) {
+            uint4 v = (a_src && k_ok) ? *reinterpret_cast<const uint4*>(a_src + k0 + lk) : zero;
+            if (GLU && scale && a_src) {
+                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const float2 f2 = __bfloat1622float2(h2[x]);
+                    h2[x] = __floats2bfloat162_rn(f2.x * a_scale, f2.y * a_scale);
+                }
+            }
+            *reinterpret_cast<uint4*>(&As[lrow][lk]) = v;
+        }
+        *reinterpret_cast<uint4*>(&Ws[lrow][lk]) =
+            (w_ok && k_ok) ? *reinterpret_cast<const uint4*>(w_src + k0 + lk) : zero;
+        if (GLU)
+            *reinterpret_cast<uint4*>(&Us[lrow][lk]) =
+                (w_ok && k_ok) ? *reinterpret_cast<const uint4*>(u_src + k0 + lk) : zero;
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < MK; kk += 16) {
+            uint32_t a[4];
+            a[0] = *reinterpret_cast<const uint32_t*>(&As[16 * wm + g][kk + c]);
+            a[1] = *reinterpret_cast<const uint32_t*>(&As[16 * wm + g + 8][kk + c]);
+            a[2] = *reinterpret_cast<const uint32_t*>(&As[16 * wm + g][kk + c + 8]);
+            a[3] = *reinterpret_cast<const uint32_t*>(&As[16 * wm + g + 8][kk + c + 8]);
+#pragma unroll
+            for (int nf = 0; nf < 2; ++nf) {
+                const int n = 16 * wn + 8 * nf + g;
+                mma_bf16(acc[nf], a, *reinterpret_cast<const uint32_t*>(&Ws[n][kk + c]),
+                         *reinterpret_cast<const uint32_t*>(&Ws[n][kk + c + 8]));
+                if (GLU)
+                    mma_bf16(acu[nf], a, *reinterpret_cast<const uint32_t*>(&Us[n][kk + c]),
+                             *reinterpret_cast<const uint32_t*>(&Us[n][kk + c + 8]));
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = 16 * wm + g + 8 * half;
+        const int slot = slot_s[r];
+        if (slot < 0) continue;
+#pragma unroll
+        for (int nf = 0; nf < 2; ++nf)
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                const int n = n0 + 16 * wn + 8 * nf + c + x;
+                if (n >= N) continue;
+                const float v = acc[nf][2 * half + x];
+                if (GLU)
+                    ((__nv_bfloat16*)out)[(size_t)(p0 + r) * N + n] =
+                        __float2bfloat16_rn((v / (1.0f + expf(-v))) * acu[nf][2 * half + x]);
+                else
+                    ((float*)out)[(size_t)slot * N + n] = scale ? v * weight[slot] : v;
+            }
+    }
+}
+
+// bfloat16 rows of whole 16-byte pieces at 16-byte addresses: the tensor-core kernel's.
+static inline bool takes_mma(int dtype, const void* a, const void* w, int K) {
+    return dtype == MLS_BF16 && K % 8 == 0 &&
+           (reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) % 16 == 0;
+}
+
 template <typename T>
 __global__ void expert_combine_kernel(const float* __restrict__ per_slot, int top,
                                       const void* __restrict__ shared, int shared_dtype,
@@ -293,7 +424,11 @@ MLS_API int mls_expert_glu(const void* h, const void* w_gate_up, void* y, int dt
                            int scale_in, int F, int K, cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
     dim3 grid((F + BN - 1) / BN, max_tiles);
-    if (dtype == MLS_BF16)
+    if (takes_mma(dtype, h, w_gate_up, K))
+        MLS_LAUNCH((expert_mma_kernel<true>), dim3(grid), dim3(256), 0, stream,
+                   (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gate_up, y, order, offsets,
+                   tile_expert, tile_row0, weight, top, scale_in, F, K);
+    else if (dtype == MLS_BF16)
         MLS_LAUNCH((expert_gemm_kernel<__nv_bfloat16, true>), dim3(grid), dim3(256), 0, stream,
                    (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gate_up, y, order, offsets,
                    tile_expert, tile_row0, weight, top, scale_in, F, K);
@@ -310,7 +445,11 @@ MLS_API int mls_expert_down(const void* y, const void* w_down, float* per_slot, 
                             int scale_out, int D, int F, cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
     dim3 grid((D + BN - 1) / BN, max_tiles);
-    if (dtype == MLS_BF16)
+    if (takes_mma(dtype, y, w_down, F))
+        MLS_LAUNCH((expert_mma_kernel<false>), dim3(grid), dim3(256), 0, stream,
+                   (const __nv_bfloat16*)y, (const __nv_bfloat16*)w_down, (void*)per_slot, order,
+                   offsets, tile_expert, tile_row0, weight, top, scale_out, D, F);
+    else if (dtype == MLS_BF16)
         MLS_LAUNCH((expert_gemm_kernel<__nv_bfloat16, false>), dim3(grid), dim3(256), 0, stream,
                    (const __nv_bfloat16*)y, (const __nv_bfloat16*)w_down, (void*)per_slot, order,
                    offsets, tile_expert, tile_row0, weight, top, scale_out, D, F);

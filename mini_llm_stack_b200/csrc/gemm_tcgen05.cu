@@ -42,7 +42,10 @@ struct GemmParams {
     int out_f32;                         // 1: out is float32
     int transposed;                      // 1: store D^T (out[n][m])
     int splits;                          // parts along K
-    int epilogue;                        // 0: store D; 1: SwiGLU over interleaved gate / up blocks of 16
+    int epilogue;                        // 0: store D; 1: gated unit over interleaved gate / up blocks of 16
+    // the gated unit: g' = min(g, limit), u' = clamp(u, -limit, limit) (limit <= 0: as they
+    // are), out = g' * sigmoid(alpha * g') * (u' + shift); SwiGLU is (1, 0, 0)
+    float glu_alpha = 1.f, glu_limit = 0.f, glu_shift = 0.f;
     int* status;
     // pairs of CTAs only: the tiles from tail_full on are cut along K into tail_parts parts of
     // tail_per k-blocks, whose raw sums go to `partial` (tail_parts <= 1: no tile is cut)
@@ -74,7 +77,14 @@ struct Smem {
     static constexpr int TOTAL = TMEM_SLOT + 16 + 1024;      // + alignment slack
 };
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+__device__ __forceinline__ float gated(float g, float u, float alpha, float limit, float shift) {
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    return (g / (1.0f + expf(-alpha * g))) * (u + shift);
+}
+#define GATED(p, g, u) gated(g, u, (p).glu_alpha, (p).glu_limit, (p).glu_shift)
 
 // Store 16 consecutive columns (col0 ..) of D's row `row`.  With the SwiGLU
 // epilogue `v` holds 16 gate columns and `u` the 16 matching up columns.
@@ -85,7 +95,7 @@ __device__ __forceinline__ void store_normal(const GemmParams& p, int row, int c
     int col = col0, width = p.nn;
     if (p.epilogue == 1) {
 #pragma unroll
-        for (int e = 0; e < 16; ++e) r[e] = silu_mul(v[e], u[e]);
+        for (int e = 0; e < 16; ++e) r[e] = GATED(p, v[e], u[e]);
         col = col0 >> 1;
         width = p.nn >> 1;
     } else {
@@ -133,7 +143,7 @@ __device__ __forceinline__ void store_transposed(const GemmParams& p, int row, i
         bool mine = true;
         if (p.epilogue == 1) {
             const float other = __shfl_xor_sync(0xffffffffu, val, 16);
-            val = silu_mul(val, other);               // meaningful in lanes 0..15
+            val = GATED(p, val, other);               // meaningful in lanes 0..15
             feature = ((row - lane) >> 1) + lane;
             width = p.mm >> 1;
             mine = lane < 16;
@@ -569,7 +579,7 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
                                 tmem_ld_wait();
 #pragma unroll
                                 for (int e = 0; e < 16; ++e)
-                                    r[b * 16 + e] = silu_mul(__uint_as_float(g[e]), __uint_as_float(u[e]));
+                                    r[b * 16 + e] = GATED(p, __uint_as_float(g[e]), __uint_as_float(u[e]));
                             }
                         } else {
                             uint32_t a[16], b[16];
@@ -655,7 +665,8 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
 // Sum of the split-K parts, then the epilogue.  Parts are [part][row][col] in the
 // order the output has ([token][feature] in both orientations).
 __global__ void splitk_sum_kernel(const float* __restrict__ partial, void* __restrict__ out,
-                                  int out_f32, int rows, int cols, int splits, int epilogue) {
+                                  int out_f32, int rows, int cols, int splits, int epilogue,
+                                  float alpha, float limit, float shift) {
     chain_release();
     chain_wait();
     const size_t n = (size_t)rows * cols;
@@ -673,7 +684,7 @@ __global__ void splitk_sum_kernel(const float* __restrict__ partial, void* __res
                 gs += partial[(size_t)k * n + g];
                 us += partial[(size_t)k * n + g + 16];
             }
-            r = silu_mul(gs, us);
+            r = gated(gs, us, alpha, limit, shift);
         } else {
             r = 0.f;
             for (int k = 0; k < splits; ++k) r += partial[(size_t)k * n + i];
@@ -710,7 +721,7 @@ __global__ void pair_tail_sum_kernel(const GemmParams p, int m_pairs, int tail_t
                 gs += src[k * part_stride + g];
                 us += src[k * part_stride + g + 16];
             }
-            v = silu_mul(gs, us);
+            v = GATED(p, gs, us);
         } else {
             v = 0.f;
 #pragma unroll 8
@@ -912,9 +923,9 @@ MLS_API long long mls_gemm_prompt_scratch_floats(int m, int n, int k) {
 // to the caller, [part][M][N]).  With swap = 0 `partial` is optional scratch of
 // mls_gemm_prompt_scratch_floats(m, n, k) floats.  epilogue 1: the weight rows alternate
 // between 16 gate rows and the 16 matching up rows, and out[M, N / 2] = silu(gate) * up.
-MLS_API int mls_gemm_bf16(const void* act, const void* w, void* out, int out_f32, int m, int n,
-                          int k, int swap, int splits, int epilogue, float* partial, int* status,
-                          cudaStream_t stream) {
+static int gemm_bf16(const void* act, const void* w, void* out, int out_f32, int m, int n, int k,
+                     int swap, int splits, int epilogue, float* partial, int* status,
+                     cudaStream_t stream, float alpha, float limit, float shift) {
     if (m <= 0 || n <= 0) return 0;
     if (k % 8 != 0 || k <= 0) return MLS_ERR_UNSUPPORTED;      // rows must be 16-byte multiples
     if (out == nullptr && (splits < 2 || !swap || epilogue != 0)) return MLS_ERR_UNSUPPORTED;
@@ -929,6 +940,9 @@ MLS_API int mls_gemm_bf16(const void* act, const void* w, void* out, int out_f32
     p.out_f32 = out_f32;
     p.splits = splits;
     p.epilogue = epilogue;
+    p.glu_alpha = alpha;
+    p.glu_limit = limit;
+    p.glu_shift = shift;
     p.status = status;
     if (swap) {
         if (m > 64) return MLS_ERR_UNSUPPORTED;
@@ -945,7 +959,7 @@ MLS_API int mls_gemm_bf16(const void* act, const void* w, void* out, int out_f32
         int blocks = (int)((total + 255) / 256);
         if (blocks > sm_count() * 8) blocks = sm_count() * 8;
         MLS_LAUNCH((splitk_sum_kernel), dim3(blocks), dim3(256), 0, stream, partial, out, out_f32,
-                   m, n, splits, epilogue);
+                   m, n, splits, epilogue, p.glu_alpha, p.glu_limit, p.glu_shift);
         return launch_status();
     }
     if (splits != 1) return MLS_ERR_UNSUPPORTED;               // prompts cut K by themselves
@@ -954,4 +968,20 @@ MLS_API int mls_gemm_bf16(const void* act, const void* w, void* out, int out_f32
     p.transposed = 0;
     if (g_prompt_kernel == 1 && m > BM) return launch_pair<6>(p, act, w, stream);
     return launch<256, 4>(p, act, w, 1, stream);
+}
+
+MLS_API int mls_gemm_bf16(const void* act, const void* w, void* out, int out_f32, int m, int n,
+                          int k, int swap, int splits, int epilogue, float* partial, int* status,
+                          cudaStream_t stream) {
+    return gemm_bf16(act, w, out, out_f32, m, n, k, swap, splits, epilogue, partial, status, stream,
+                     1.f, 0.f, 0.f);
+}
+
+// The same with epilogue 1 as another gated unit: out = g' * sigmoid(alpha * g') * (u' + shift)
+// with g' = min(gate, limit), u' = clamp(up, -limit, limit) (limit <= 0: no clamping).
+MLS_API int mls_gemm_bf16_gated(const void* act, const void* w, void* out, int out_f32, int m,
+                                int n, int k, int swap, int splits, float alpha, float limit,
+                                float shift, float* partial, int* status, cudaStream_t stream) {
+    return gemm_bf16(act, w, out, out_f32, m, n, k, swap, splits, 1, partial, status, stream, alpha,
+                     limit, shift);
 }

@@ -15,7 +15,7 @@
 // sigmoid(gate) and rounds once to the activation type.
 //
 // A CTA owns FC columns of one head's C for one request and keeps them in registers:
-// thread (col, eg) holds the rows eg, eg + EG, ... of its column.  Only the CTA of a
+// thread (col, eg) holds a run of rows of its column.  Only the CTA of a
 // head's first columns carries n (a thread holds the elements tid, tid + 256, ...); every
 // CTA carries its own copy of m (the state row of a head is
 // [C (e*f) | n (e) | m (one per column group)]), so no CTA reads what another writes.
@@ -30,7 +30,7 @@
 
 namespace {
 constexpr int SCAN_THREADS = 256;
-constexpr int TB = 8;                       // tokens a pass
+constexpr int TB = 16;                      // tokens a pass
 constexpr int MAXN = 4;                     // elements of n a thread holds: e <= 1024
 
 __device__ __forceinline__ float soft_cap(float z, float cap) { return cap * tanhf(z / cap); }
@@ -38,9 +38,25 @@ __device__ __forceinline__ float log_sigmoid(float z) {
     return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
 }
 
+// 16 bytes of a row as floats.
+__device__ __forceinline__ void load16(const float* p, float (&out)[4]) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+}
+__device__ __forceinline__ void load16(const __nv_bfloat16* p, float (&out)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+        const float2 f2 = __bfloat1622float2(h[x]);
+        out[2 * x] = f2.x;
+        out[2 * x + 1] = f2.y;
+    }
+}
+
 // MAXR: most rows of C a thread holds.
 template <typename T, int MAXR>
-__global__ void __launch_bounds__(SCAN_THREADS)
+__global__ void __launch_bounds__(SCAN_THREADS, MAXR <= 16 ? 2 : 1)
 mlstm_scan_kernel(const T* __restrict__ qkvg, int row_w, int q_off, int k_off, int v_off,
                   const float* __restrict__ gates /* [T, 2H]: zi | zf */,
                   const void* __restrict__ bias_i, const void* __restrict__ bias_f, int b_dtype,
@@ -68,11 +84,15 @@ mlstm_scan_kernel(const T* __restrict__ qkvg, int row_w, int q_off, int k_off, i
     const int t0 = cu_q[req], t1 = cu_q[req + 1];
     float* st = state + (size_t)state_slot[req] * slot_stride +
                 (size_t)head * ((size_t)e * f + e + n_groups);
+    // a thread's rows lie side by side, so that k and q come from shared memory four at a time
+    const int rows_per = (e + eg_count - 1) / eg_count;
+    const int row0 = eg * rows_per;
+    const bool vec = (rows_per & 3) == 0 && (e & 3) == 0;
     float C[MAXR];
 #pragma unroll
     for (int r = 0; r < MAXR; ++r) {
-        const int row = eg + r * eg_count;
-        C[r] = (active && row < e) ? st[(size_t)row * f + gcol] : 0.f;
+        const int row = row0 + r;
+        C[r] = (active && r < rows_per && row < e) ? st[(size_t)row * f + gcol] : 0.f;
     }
     float nreg[MAXN];
 #pragma unroll
@@ -83,15 +103,34 @@ mlstm_scan_kernel(const T* __restrict__ qkvg, int row_w, int q_off, int k_off, i
     float m = st[(size_t)e * f + e + grp];
     const float bi = load_as_float(bias_i, head, b_dtype), bf = load_as_float(bias_f, head, b_dtype);
     const float q_scale = 1.0f / sqrtf((float)e);
+    constexpr int V = 16 / (int)sizeof(T);
+    const bool vload = e % V == 0 && row_w % V == 0 && q_off % V == 0 && k_off % V == 0 &&
+                       reinterpret_cast<uintptr_t>(qkvg) % 16 == 0;
 
     for (int tb = t0; tb < t1; tb += TB) {
         const int nb = min(TB, t1 - tb);
-        // ---- the block's inputs
-        for (int u = threadIdx.x; u < nb * e; u += SCAN_THREADS) {
-            const int j = u / e, i = u - j * e;
-            const T* row = qkvg + (size_t)(tb + j) * row_w;
-            q_s[j * e + i] = Elem<T>::load(row + q_off + head * e + i) * q_scale;
-            k_s[j * e + i] = Elem<T>::load(row + k_off + head * e + i);
+        // ---- the block's inputs (16 bytes a load where the layout allows)
+        if (vload) {
+            const int per_row = e / V;
+            for (int u = threadIdx.x; u < nb * per_row; u += SCAN_THREADS) {
+                const int j = u / per_row, i = (u - j * per_row) * V;
+                const T* row = qkvg + (size_t)(tb + j) * row_w + head * e + i;
+                float qv[V], kv[V];
+                load16(row + q_off, qv);
+                load16(row + k_off, kv);
+#pragma unroll
+                for (int x = 0; x < V; ++x) {
+                    q_s[j * e + i + x] = qv[x] * q_scale;
+                    k_s[j * e + i + x] = kv[x];
+                }
+            }
+        } else {
+            for (int u = threadIdx.x; u < nb * e; u += SCAN_THREADS) {
+                const int j = u / e, i = u - j * e;
+                const T* row = qkvg + (size_t)(tb + j) * row_w;
+                q_s[j * e + i] = Elem<T>::load(row + q_off + head * e + i) * q_scale;
+                k_s[j * e + i] = Elem<T>::load(row + k_off + head * e + i);
+            }
         }
         for (int u = threadIdx.x; u < nb * fc; u += SCAN_THREADS) {
             const int j = u / fc, c = u - j * fc;
@@ -118,16 +157,35 @@ mlstm_scan_kernel(const T* __restrict__ qkvg, int row_w, int q_off, int k_off, i
                 const float tv = take * v_s[j * fc + col];
                 const float* kj = k_s + j * e;
                 const float* qj = q_s + j * e;
-                float o = 0.f;
+                // four sums side by side (the order is fixed by the row's place, not by the data)
+                float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+                if (vec) {
 #pragma unroll
-                for (int r = 0; r < MAXR; ++r) {
-                    const int rr = eg + r * eg_count;
-                    if (rr < e) {
-                        C[r] = fmaf(keep, C[r], kj[rr] * tv);
-                        o = fmaf(C[r], qj[rr], o);
+                    for (int r = 0; r < MAXR; r += 4) {
+                        if (r < rows_per && row0 + r < e) {
+                            const float4 k4 = *reinterpret_cast<const float4*>(kj + row0 + r);
+                            const float4 q4 = *reinterpret_cast<const float4*>(qj + row0 + r);
+                            C[r] = fmaf(keep, C[r], k4.x * tv);
+                            C[r + 1] = fmaf(keep, C[r + 1], k4.y * tv);
+                            C[r + 2] = fmaf(keep, C[r + 2], k4.z * tv);
+                            C[r + 3] = fmaf(keep, C[r + 3], k4.w * tv);
+                            o0 = fmaf(C[r], q4.x, o0);
+                            o1 = fmaf(C[r + 1], q4.y, o1);
+                            o2 = fmaf(C[r + 2], q4.z, o2);
+                            o3 = fmaf(C[r + 3], q4.w, o3);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int r = 0; r < MAXR; ++r) {
+                        const int rr = row0 + r;
+                        if (r < rows_per && rr < e) {
+                            C[r] = fmaf(keep, C[r], kj[rr] * tv);
+                            o0 = fmaf(C[r], qj[rr], o0);
+                        }
                     }
                 }
-                part[(j * eg_count + eg) * fc + col] = o;
+                part[(j * eg_count + eg) * fc + col] = (o0 + o1) + (o2 + o3);
             }
             if (first) {
                 float nq = 0.f;
@@ -163,8 +221,8 @@ mlstm_scan_kernel(const T* __restrict__ qkvg, int row_w, int q_off, int k_off, i
     }
 #pragma unroll
     for (int r = 0; r < MAXR; ++r) {
-        const int row = eg + r * eg_count;
-        if (active && row < e) st[(size_t)row * f + gcol] = C[r];
+        const int row = row0 + r;
+        if (active && r < rows_per && row < e) st[(size_t)row * f + gcol] = C[r];
     }
     if (first) {
 #pragma unroll
@@ -247,11 +305,10 @@ int pick_scan(int maxr, const void* qkvg, int row_w, int q_off, int k_off, int v
 }  // namespace
 
 // Columns of C a CTA owns for heads of (e, f): as many as leave a thread at most 64 rows,
-// at most 32 (a warp then reads one row of k and q at a time, and one prompt makes enough
-// CTAs for the GPU) and at most f.  The state row of a head is e*f + e + ceil(f / columns)
+// at most 16 (one prompt then makes enough CTAs for the GPU, two to an SM) and at most f.  The state row of a head is e*f + e + ceil(f / columns)
 // floats.
 MLS_API int mls_mlstm_columns(int e, int f) {
-    int fc = f < 32 ? f : 32;
+    int fc = f < 16 ? f : 16;
     while (fc > 1 && (e + (SCAN_THREADS / fc) - 1) / (SCAN_THREADS / fc) > 64) fc = (fc + 1) / 2;
     return fc;
 }

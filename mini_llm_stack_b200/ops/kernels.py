@@ -328,6 +328,8 @@ class Ops:
             lib = self._load("gemm")
             self._gemm = _decl(lib, "mls_gemm_bf16",
                                [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _P, _P])
+            self._gemm_gated = _decl(lib, "mls_gemm_bf16_gated",
+                                     [_P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _F, _F, _P, _P, _P])
             self._gemm_prompt_scratch = _decl(lib, "mls_gemm_prompt_scratch_floats", [_I, _I, _I],
                                               restype=ctypes.c_longlong)
             self._gemm_lib = lib
@@ -342,7 +344,7 @@ class Ops:
         fn(("never", "auto", "always").index(mode))
 
     def _gemm_bf16(self, a, w, out, m: int, n: int, k: int, epilogue: int = 0,
-                   leave_parts: bool = False):
+                   leave_parts: bool = False, gate=None):
         """The tcgen05 product.  ``leave_parts``: the K-parts are not added up but
         returned as ``SplitParts`` (the caller has checked that there are several)."""
         self._gemm_library()
@@ -370,6 +372,11 @@ class Ops:
         _need(not leave_parts or splits > 1, "gemm_bf16: no parts to leave")
         self.launches += 1 + sums
         out_f32 = 1 if (out is not None and out.dtype == torch.float32) else 0
+        if gate is not None:          # epilogue 1 with another gated unit: (alpha, limit, shift)
+            _check(self._gemm_gated(_ptr(a), _ptr(w), _ptr(out), out_f32, m, n, k, swap, splits,
+                                    float(gate[0]), float(gate[1]), float(gate[2]), _ptr(partial),
+                                    _ptr(self.status), self._stream()), "gemm_bf16_gated")
+            return None
         _check(self._gemm(_ptr(a), _ptr(w), None if leave_parts else _ptr(out), out_f32,
                           m, n, k, swap, splits, epilogue, _ptr(partial), _ptr(self.status),
                           self._stream()), "gemm_bf16")
@@ -418,6 +425,20 @@ class Ops:
         if m == 0:
             return
         self._gemm_bf16(a, w_interleaved, out, m, n, k, epilogue=1)
+
+    def linear_clamped_glu(self, a, w_interleaved, out, alpha: float, limit: float) -> None:
+        """``out[M, I] = g' * sigmoid(alpha * g') * (u' + 1)`` with ``g' = min(a @ Wg^T, limit)``
+        and ``u' = clamp(a @ Wu^T, -limit, limit)`` in one kernel; the weight as for
+        ``linear_swiglu`` (``interleave_gate_up``)."""
+        m, k = a.shape
+        n = w_interleaved.shape[0]
+        _need(out.shape == (m, n // 2) and a.dtype == torch.bfloat16 and
+              w_interleaved.dtype == torch.bfloat16, "linear_clamped_glu: shapes or types")
+        _need(a.is_contiguous() and w_interleaved.is_contiguous() and out.is_contiguous(),
+              "linear_clamped_glu: operands must be contiguous")
+        if m == 0:
+            return
+        self._gemm_bf16(a, w_interleaved, out, m, n, k, epilogue=1, gate=(alpha, limit, 1.0))
 
     def rope_takes_parts(self, hd: int) -> bool:
         """Whether ``rope_store`` can read its rows from a product's K-parts."""

@@ -63,7 +63,8 @@ class SwiGLUFeedForward(FeedForward):
 class ClampedGLUFeedForward(FeedForward):
     """``W_down (g' * sigmoid(alpha * g') * (u' + 1))`` with ``g' = min(W_gate h, limit)``
     and ``u' = clamp(W_up h, -limit, limit)``; no biases.  The activation runs in
-    float32 on the projection's output."""
+    float32, in the projection's own epilogue where the tcgen05 kernel takes the sizes
+    (as ``SwiGLUFeedForward`` does), else on the projection's output."""
 
     decode_capturable = prompt_capturable = True
 
@@ -81,16 +82,25 @@ class ClampedGLUFeedForward(FeedForward):
     def bind(self, tensors: dict, runtime) -> None:
         self.runtime = runtime
         g, u, dn = self.names
-        self.w_gate_up = runtime.ops.prepare_weight(torch.cat([tensors[g], tensors[u]], dim=0))
-        self.w_down = runtime.ops.prepare_weight(tensors[dn])
+        ops = runtime.ops
+        self.fused = (tensors[g].dtype == torch.bfloat16 and tensors[u].dtype == torch.bfloat16
+                      and ops.can_fuse_swiglu(self.d_model, self.intermediate_size))
+        if self.fused:
+            self.w_gate_up = ops.prepare_weight(ops.interleave_gate_up(tensors[g], tensors[u]))
+        else:
+            self.w_gate_up = ops.prepare_weight(torch.cat([tensors[g], tensors[u]], dim=0))
+        self.w_down = ops.prepare_weight(tensors[dn])
 
     def forward(self, h, step: StepContext):
         rt = self.runtime
         t, i = h.shape[0], self.intermediate_size
-        gu = rt.buffer("gate_up", (t, 2 * i), rt.act_dtype)
-        rt.ops.linear(h, self.w_gate_up, gu)
         act = rt.buffer("ffn_act", (t, i), rt.act_dtype)
-        rt.ops.clamped_glu(gu, act, self.alpha, self.limit)
+        if self.fused:
+            rt.ops.linear_clamped_glu(h, self.w_gate_up, act, self.alpha, self.limit)
+        else:
+            gu = rt.buffer("gate_up", (t, 2 * i), rt.act_dtype)
+            rt.ops.linear(h, self.w_gate_up, gu)
+            rt.ops.clamped_glu(gu, act, self.alpha, self.limit)
         delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)
         return rt.ops.linear_parts(act, self.w_down, delta)
 

@@ -25,9 +25,9 @@ from .base import CacheHandle, FixedState, Mixer, StepContext, TensorSpec
 
 def state_columns(e: int, f: int, threads: int = 256, most_rows: int = 64) -> int:
     """Columns of a head's memory one CTA of the scan kernel owns (the kernel's own rule,
-    restated so that the state's size is known without a device): at most 32, at most f,
+    restated so that the state's size is known without a device): at most 16, at most f,
     halved until a thread holds at most ``most_rows`` of the e rows."""
-    fc = min(f, 32)
+    fc = min(f, 16)
     while fc > 1 and -(-e // (threads // fc)) > most_rows:
         fc = (fc + 1) // 2
     return fc

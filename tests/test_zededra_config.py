@@ -62,8 +62,8 @@ def test_tensor_names_and_cache_slots():
     specs = model.cache_specs()
     assert len(specs) == 11                                  # one slot a layer run
     assert specs[0] == PagedKV(1, 48, None, shared_kv=True)  # a latent of 40 in rows of 48
-    assert specs[1] == FixedState((2, 24 * 40 + 24 + 2), torch.float32)  # 40 columns: two groups
-    assert specs[3] == FixedState((4, 8 * 80 + 8 + 3), torch.float32)    # 80 columns: three groups
+    assert specs[1] == FixedState((2, 24 * 40 + 24 + 3), torch.float32)  # 40 columns: three groups
+    assert specs[3] == FixedState((4, 8 * 80 + 8 + 5), torch.float32)    # 80 columns: five groups
     assert specs[1] == specs[4] == specs[7]                  # every pass its own slot, same shape
     # the cache manager groups them: latents of equal width share pages, every pass has its own pool
     cache = CacheManager(specs, num_blocks=4, block_size=8, max_requests=2, max_seq_len=32,
@@ -76,7 +76,7 @@ def test_tensor_names_and_cache_slots():
 def test_state_columns_leave_a_thread_at_most_64_rows():
     for e, f in [(8, 80), (32, 48), (256, 512), (1024, 64), (40, 150), (4096, 16)]:
         fc = state_columns(e, f)
-        assert 1 <= fc <= min(f, 32) and -(-e // (256 // fc)) <= 64
+        assert 1 <= fc <= min(f, 16) and -(-e // (256 // fc)) <= 64
 
 
 def test_plain_mlstm_carries_its_state():
