@@ -65,9 +65,9 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W, float*
 
 // Few output columns (a router's or a gate's scores: N <= SKINNY_N): the tile kernel above
 // would leave all but a few SMs idle and walk K in steps of 16 behind two barriers each.
-// Here a block holds SK_ROWS rows of A in shared memory, a warp owns the output columns
-// n = warp, warp + 8, ... and its lanes walk K with a stride of 32; the 32 partial sums are
-// added by a fixed tree.  The order of the additions depends on K alone (never on M or on
+// Here a block holds SK_ROWS rows of A in shared memory, each of its eight warps owns one of
+// eight output columns (blockIdx.y names the eight) and its lanes walk K with a stride of 32;
+// the 32 partial sums are added by a fixed tree.  The order of the additions depends on K alone (never on M or on
 // the row's place in its block), and which kernel runs depends on N alone, so a token's
 // result still does not depend on its batch.
 constexpr int SKINNY_N = 64, SK_ROWS = 8, SK_KC = 1024;
@@ -80,8 +80,8 @@ gemm_f32_skinny_kernel(const float* __restrict__ A, const float* __restrict__ W,
     __shared__ float As[SK_ROWS][SK_KC];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * SK_ROWS;
-    for (int n0 = 0; n0 < N; n0 += 8) {
-        const int n = n0 + warp;
+    {
+        const int n = blockIdx.y * 8 + warp;
         float acc[SK_ROWS];
 #pragma unroll
         for (int r = 0; r < SK_ROWS; ++r) acc[r] = 0.f;
@@ -115,8 +115,8 @@ MLS_API int mls_gemm_f32(const float* A, const float* W, float* out, int M, int 
                          cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (N <= SKINNY_N) {
-        MLS_LAUNCH((gemm_f32_skinny_kernel), dim3((M + SK_ROWS - 1) / SK_ROWS), dim3(256), 0,
-                   stream, A, W, out, M, N, K);
+        MLS_LAUNCH((gemm_f32_skinny_kernel), dim3((M + SK_ROWS - 1) / SK_ROWS, (N + 7) / 8),
+                   dim3(256), 0, stream, A, W, out, M, N, K);
         return launch_status();
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
