@@ -119,9 +119,11 @@ mlstm_scan_kernel(const T* __restrict__ qkvg, int row_w, int q_off, int k_off, i
                 load16(row + q_off, qv);
                 load16(row + k_off, kv);
 #pragma unroll
-                for (int x = 0; x < V; ++x) {
-                    q_s[j * e + i + x] = qv[x] * q_scale;
-                    k_s[j * e + i + x] = kv[x];
+                for (int x = 0; x < V; x += 4) {         // e and i are multiples of 4: 16-byte stores
+                    *reinterpret_cast<float4*>(q_s + j * e + i + x) = make_float4(
+                        qv[x] * q_scale, qv[x + 1] * q_scale, qv[x + 2] * q_scale, qv[x + 3] * q_scale);
+                    *reinterpret_cast<float4*>(k_s + j * e + i + x) =
+                        make_float4(kv[x], kv[x + 1], kv[x + 2], kv[x + 3]);
                 }
             }
         } else {
@@ -146,7 +148,7 @@ mlstm_scan_kernel(const T* __restrict__ qkvg, int row_w, int q_off, int k_off, i
         __syncthreads();
         // ---- token by token: the stabiliser (walked by every thread for itself), C and the
         // token's partial output, n and the partial n . q
-#pragma unroll 1
+#pragma unroll 2
         for (int j = 0; j < nb; ++j) {
             const float ig = gate_s[j], fg = gate_s[TB + j];
             const float m_new = fmaxf(fg + m, ig);
