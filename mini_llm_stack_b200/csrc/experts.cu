@@ -252,8 +252,8 @@ expert_gemm_kernel(const T* __restrict__ A, const T* __restrict__ W, void* __res
 }
 
 // The same products for bfloat16 on the tensor cores (mma.sync m16n8k16, float32
-// accumulators): a CTA takes the same tile of 32 sorted rows x 64 output columns, its eight
-// warps 16 x 16 each; operands go through shared memory in rows of 32 + 8 values, so that
+// accumulators): a CTA takes up to four of the same tiles of 32 sorted rows x 64 output
+// columns, its eight warps 32 x 32 each; operands go through shared memory in rows of 32 + 8 values, so that
 // the fragment loads (one 32-bit word a lane) meet no bank twice.  Every output element is
 // its own dot product over k ascending in steps of 16, whatever else is in the tile.  With
 // input scaling the row is rounded to bfloat16 once more after the weight is applied.
@@ -268,109 +268,149 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <bool GLU>
+// A CTA walks RT consecutive entries of the tile list; entries of one expert that follow each
+// other (a prompt gives an expert many rows) are taken together, up to RT * 32 = 128 rows
+// against one load of every weight tile; rows that are not there are zeros.
+// RT = 1 (few rows an expert: decoding) keeps one entry a CTA, so that as many CTAs as
+// possible stream weights.
+template <bool GLU, int RT>
 __global__ void __launch_bounds__(256)
 expert_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                   void* __restrict__ out, const int* __restrict__ order,
                   const int* __restrict__ offsets, const int* __restrict__ tile_expert,
-                  const int* __restrict__ tile_row0, const float* __restrict__ weight, int top,
-                  int scale, int N, int K) {
+                  const int* __restrict__ tile_row0, int max_tiles,
+                  const float* __restrict__ weight, int top, int scale, int N, int K) {
     chain_release();
     chain_wait();
-    const int e = tile_expert[blockIdx.y];
-    if (e < 0) return;
-    __shared__ __align__(16) __nv_bfloat16 As[BM][MKP];
+    constexpr int MROWS = RT * BM;
+    // RT 4: 4 x 2 warps of 32 rows x 32 columns; RT 1: 2 x 4 warps of 16 x 16
+    constexpr int MF = RT == 4 ? 2 : 1, NF = RT == 4 ? 4 : 2, WARPS_N = RT == 4 ? 2 : 4;
+    constexpr int LOADS = (MROWS * 4 + 255) / 256;            // 16-byte pieces of A a thread loads
+    __shared__ __align__(16) __nv_bfloat16 As[MROWS][MKP];
     __shared__ __align__(16) __nv_bfloat16 Ws[BN][MKP];
     __shared__ __align__(16) __nv_bfloat16 Us[GLU ? BN : 1][MKP];
-    __shared__ int slot_s[BM];
+    __shared__ int slot_s[MROWS];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int p0 = tile_row0[blockIdx.y], p_end = offsets[e + 1];
     const int n0 = blockIdx.x * BN;
-    if (tid < BM) slot_s[tid] = p0 + tid < p_end ? order[p0 + tid] : -1;
-    __syncthreads();
-    const __nv_bfloat16* We = W + (size_t)e * (GLU ? 2 : 1) * N * K;
-    const int wm = warp >> 2, wn = warp & 3;                  // 2 x 4 warps of 16 x 16
+    const int wm = warp / WARPS_N, wn = warp % WARPS_N;
     const int g = lane >> 2, c = (lane & 3) * 2;
-    float acc[2][4], acu[2][4];
-#pragma unroll
-    for (int i = 0; i < 2; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = acu[i][j] = 0.f;
-    // who loads what: 16 bytes a thread and tile
-    const int lrow = tid >> 2, lk = (tid & 3) * 8;
-    const __nv_bfloat16* a_src = nullptr;
-    float a_scale = 1.f;
-    if (tid < BM * 4) {
-        const int slot = slot_s[lrow];
-        if (slot >= 0) {
-            if (GLU) {
-                a_src = A + (size_t)(slot / top) * K;
-                if (scale) a_scale = weight[slot];
-            } else {
-                a_src = A + (size_t)(p0 + lrow) * K;
-            }
-        }
-    }
-    const bool w_ok = n0 + lrow < N;
-    const __nv_bfloat16* w_src = We + (size_t)(n0 + lrow) * K;
-    const __nv_bfloat16* u_src = We + (size_t)(N + n0 + lrow) * K;
+    const int lrow = tid >> 2, lk = (tid & 3) * 8;            // who loads what: 16 bytes a thread
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    for (int k0 = 0; k0 < K; k0 += MK) {
-        const bool k_ok = k0 + lk < K;
-        if (tid < BM * 4) {
-            uint4 v = (a_src && k_ok) ? *reinterpret_cast<const uint4*>(a_src + k0 + lk) : zero;
-            if (GLU && scale && a_src) {
-                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&v);
+    const int t_end = min(max_tiles, (int)(blockIdx.y + 1) * RT);   // every output element is the same sum for either RT
+    int t = blockIdx.y * RT;
+    while (t < t_end) {
+        const int e = tile_expert[t];
+        if (e < 0) break;                                     // the list's unused tail
+        int run = 1;
+        while (t + run < t_end && tile_expert[t + run] == e) ++run;
+        const int p0 = tile_row0[t], p_end = offsets[e + 1];
+        t += run;
+        __syncthreads();                                      // the last run's slot_s is read no more
+        if (tid < MROWS) slot_s[tid] = (tid < run * BM && p0 + tid < p_end) ? order[p0 + tid] : -1;
+        __syncthreads();
+        const __nv_bfloat16* We = W + (size_t)e * (GLU ? 2 : 1) * N * K;
+        float acc[MF][NF][4], acu[GLU ? MF : 1][NF][4];
+#pragma unroll
+        for (int i = 0; i < MF; ++i)
+#pragma unroll
+            for (int j = 0; j < NF; ++j)
 #pragma unroll
                 for (int x = 0; x < 4; ++x) {
-                    const float2 f2 = __bfloat1622float2(h2[x]);
-                    h2[x] = __floats2bfloat162_rn(f2.x * a_scale, f2.y * a_scale);
+                    acc[i][j][x] = 0.f;
+                    if (GLU) acu[i][j][x] = 0.f;
+                }
+        const __nv_bfloat16* a_src[LOADS];
+        float a_scale[LOADS];
+#pragma unroll
+        for (int h2 = 0; h2 < LOADS; ++h2) {
+            const int r = lrow + 64 * h2;
+            const int slot = r < MROWS ? slot_s[r] : -1;
+            a_src[h2] = nullptr;
+            a_scale[h2] = 1.f;
+            if (slot >= 0) {
+                if (GLU) {
+                    a_src[h2] = A + (size_t)(slot / top) * K;
+                    if (scale) a_scale[h2] = weight[slot];
+                } else {
+                    a_src[h2] = A + (size_t)(p0 + r) * K;
                 }
             }
-            *reinterpret_cast<uint4*>(&As[lrow][lk]) = v;
         }
-        *reinterpret_cast<uint4*>(&Ws[lrow][lk]) =
-            (w_ok && k_ok) ? *reinterpret_cast<const uint4*>(w_src + k0 + lk) : zero;
-        if (GLU)
-            *reinterpret_cast<uint4*>(&Us[lrow][lk]) =
-                (w_ok && k_ok) ? *reinterpret_cast<const uint4*>(u_src + k0 + lk) : zero;
-        __syncthreads();
+        const bool w_ok = n0 + lrow < N;
+        const __nv_bfloat16* w_src = We + (size_t)(n0 + lrow) * K;
+        const __nv_bfloat16* u_src = We + (size_t)(N + n0 + lrow) * K;
+        for (int k0 = 0; k0 < K; k0 += MK) {
+            const bool k_ok = k0 + lk < K;
 #pragma unroll
-        for (int kk = 0; kk < MK; kk += 16) {
-            uint32_t a[4];
-            a[0] = *reinterpret_cast<const uint32_t*>(&As[16 * wm + g][kk + c]);
-            a[1] = *reinterpret_cast<const uint32_t*>(&As[16 * wm + g + 8][kk + c]);
-            a[2] = *reinterpret_cast<const uint32_t*>(&As[16 * wm + g][kk + c + 8]);
-            a[3] = *reinterpret_cast<const uint32_t*>(&As[16 * wm + g + 8][kk + c + 8]);
+            for (int h2 = 0; h2 < LOADS; ++h2) {
+                if (lrow + 64 * h2 >= MROWS) continue;
+                uint4 v = (a_src[h2] && k_ok) ? *reinterpret_cast<const uint4*>(a_src[h2] + k0 + lk) : zero;
+                if (GLU && scale && a_src[h2]) {
+                    __nv_bfloat162* p2 = reinterpret_cast<__nv_bfloat162*>(&v);
 #pragma unroll
-            for (int nf = 0; nf < 2; ++nf) {
-                const int n = 16 * wn + 8 * nf + g;
-                mma_bf16(acc[nf], a, *reinterpret_cast<const uint32_t*>(&Ws[n][kk + c]),
-                         *reinterpret_cast<const uint32_t*>(&Ws[n][kk + c + 8]));
-                if (GLU)
-                    mma_bf16(acu[nf], a, *reinterpret_cast<const uint32_t*>(&Us[n][kk + c]),
-                             *reinterpret_cast<const uint32_t*>(&Us[n][kk + c + 8]));
+                    for (int x = 0; x < 4; ++x) {
+                        const float2 f2 = __bfloat1622float2(p2[x]);
+                        p2[x] = __floats2bfloat162_rn(f2.x * a_scale[h2], f2.y * a_scale[h2]);
+                    }
+                }
+                *reinterpret_cast<uint4*>(&As[lrow + 64 * h2][lk]) = v;
             }
+            *reinterpret_cast<uint4*>(&Ws[lrow][lk]) =
+                (w_ok && k_ok) ? *reinterpret_cast<const uint4*>(w_src + k0 + lk) : zero;
+            if (GLU)
+                *reinterpret_cast<uint4*>(&Us[lrow][lk]) =
+                    (w_ok && k_ok) ? *reinterpret_cast<const uint4*>(u_src + k0 + lk) : zero;
+            __syncthreads();
+            if (16 * MF * wm < run * BM) {                    // a warp whose rows are not there idles
+#pragma unroll
+                for (int kk = 0; kk < MK; kk += 16) {
+                    uint32_t a[MF][4];
+#pragma unroll
+                    for (int mf = 0; mf < MF; ++mf) {
+                        const int r = 16 * MF * wm + 16 * mf + g;
+                        a[mf][0] = *reinterpret_cast<const uint32_t*>(&As[r][kk + c]);
+                        a[mf][1] = *reinterpret_cast<const uint32_t*>(&As[r + 8][kk + c]);
+                        a[mf][2] = *reinterpret_cast<const uint32_t*>(&As[r][kk + c + 8]);
+                        a[mf][3] = *reinterpret_cast<const uint32_t*>(&As[r + 8][kk + c + 8]);
+                    }
+#pragma unroll
+                    for (int nf = 0; nf < NF; ++nf) {
+                        const int n = 8 * NF * wn + 8 * nf + g;
+                        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(&Ws[n][kk + c]);
+                        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(&Ws[n][kk + c + 8]);
+#pragma unroll
+                        for (int mf = 0; mf < MF; ++mf) mma_bf16(acc[mf][nf], a[mf], b0, b1);
+                        if (GLU) {
+                            const uint32_t u0 = *reinterpret_cast<const uint32_t*>(&Us[n][kk + c]);
+                            const uint32_t u1 = *reinterpret_cast<const uint32_t*>(&Us[n][kk + c + 8]);
+#pragma unroll
+                            for (int mf = 0; mf < MF; ++mf) mma_bf16(acu[mf][nf], a[mf], u0, u1);
+                        }
+                    }
+                }
+            }
+            __syncthreads();
         }
-        __syncthreads();
-    }
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const int r = 16 * wm + g + 8 * half;
-        const int slot = slot_s[r];
-        if (slot < 0) continue;
+        for (int mf = 0; mf < MF; ++mf)
 #pragma unroll
-        for (int nf = 0; nf < 2; ++nf)
+            for (int half = 0; half < 2; ++half) {
+                const int r = 16 * MF * wm + 16 * mf + g + 8 * half;
+                const int slot = slot_s[r];
+                if (slot < 0) continue;
 #pragma unroll
-            for (int x = 0; x < 2; ++x) {
-                const int n = n0 + 16 * wn + 8 * nf + c + x;
-                if (n >= N) continue;
-                const float v = acc[nf][2 * half + x];
-                if (GLU)
-                    ((__nv_bfloat16*)out)[(size_t)(p0 + r) * N + n] =
-                        __float2bfloat16_rn((v / (1.0f + expf(-v))) * acu[nf][2 * half + x]);
-                else
-                    ((float*)out)[(size_t)slot * N + n] = scale ? v * weight[slot] : v;
+                for (int nf = 0; nf < NF; ++nf)
+#pragma unroll
+                    for (int x = 0; x < 2; ++x) {
+                        const int n = n0 + 8 * NF * wn + 8 * nf + c + x;
+                        if (n >= N) continue;
+                        const float v = acc[mf][nf][2 * half + x];
+                        if (GLU)
+                            ((__nv_bfloat16*)out)[(size_t)(p0 + r) * N + n] = __float2bfloat16_rn(
+                                (v / (1.0f + expf(-v))) * acu[mf][nf][2 * half + x]);
+                        else
+                            ((float*)out)[(size_t)slot * N + n] = scale ? v * weight[slot] : v;
+                    }
             }
     }
 }
@@ -421,13 +461,17 @@ MLS_API int mls_route_sort(const int* idx, int n_slots, int n_experts, int* orde
 MLS_API int mls_expert_glu(const void* h, const void* w_gate_up, void* y, int dtype,
                            const int* order, const int* offsets, const int* tile_expert,
                            const int* tile_row0, int max_tiles, const float* weight, int top,
-                           int scale_in, int F, int K, cudaStream_t stream) {
+                           int scale_in, int F, int K, int many_rows, cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
     dim3 grid((F + BN - 1) / BN, max_tiles);
-    if (takes_mma(dtype, h, w_gate_up, K))
-        MLS_LAUNCH((expert_mma_kernel<true>), dim3(grid), dim3(256), 0, stream,
+    if (takes_mma(dtype, h, w_gate_up, K) && many_rows)
+        MLS_LAUNCH((expert_mma_kernel<true, 4>), dim3(grid.x, (max_tiles + 3) / 4), dim3(256), 0,
+                   stream, (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gate_up, y, order, offsets,
+                   tile_expert, tile_row0, max_tiles, weight, top, scale_in, F, K);
+    else if (takes_mma(dtype, h, w_gate_up, K))
+        MLS_LAUNCH((expert_mma_kernel<true, 1>), dim3(grid), dim3(256), 0, stream,
                    (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gate_up, y, order, offsets,
-                   tile_expert, tile_row0, weight, top, scale_in, F, K);
+                   tile_expert, tile_row0, max_tiles, weight, top, scale_in, F, K);
     else if (dtype == MLS_BF16)
         MLS_LAUNCH((expert_gemm_kernel<__nv_bfloat16, true>), dim3(grid), dim3(256), 0, stream,
                    (const __nv_bfloat16*)h, (const __nv_bfloat16*)w_gate_up, y, order, offsets,
@@ -442,13 +486,17 @@ MLS_API int mls_expert_glu(const void* h, const void* w_gate_up, void* y, int dt
 MLS_API int mls_expert_down(const void* y, const void* w_down, float* per_slot, int dtype,
                             const int* order, const int* offsets, const int* tile_expert,
                             const int* tile_row0, int max_tiles, const float* weight, int top,
-                            int scale_out, int D, int F, cudaStream_t stream) {
+                            int scale_out, int D, int F, int many_rows, cudaStream_t stream) {
     if (max_tiles <= 0) return 0;
     dim3 grid((D + BN - 1) / BN, max_tiles);
-    if (takes_mma(dtype, y, w_down, F))
-        MLS_LAUNCH((expert_mma_kernel<false>), dim3(grid), dim3(256), 0, stream,
+    if (takes_mma(dtype, y, w_down, F) && many_rows)
+        MLS_LAUNCH((expert_mma_kernel<false, 4>), dim3(grid.x, (max_tiles + 3) / 4), dim3(256), 0,
+                   stream, (const __nv_bfloat16*)y, (const __nv_bfloat16*)w_down, (void*)per_slot,
+                   order, offsets, tile_expert, tile_row0, max_tiles, weight, top, scale_out, D, F);
+    else if (takes_mma(dtype, y, w_down, F))
+        MLS_LAUNCH((expert_mma_kernel<false, 1>), dim3(grid), dim3(256), 0, stream,
                    (const __nv_bfloat16*)y, (const __nv_bfloat16*)w_down, (void*)per_slot, order,
-                   offsets, tile_expert, tile_row0, weight, top, scale_out, D, F);
+                   offsets, tile_expert, tile_row0, max_tiles, weight, top, scale_out, D, F);
     else if (dtype == MLS_BF16)
         MLS_LAUNCH((expert_gemm_kernel<__nv_bfloat16, false>), dim3(grid), dim3(256), 0, stream,
                    (const __nv_bfloat16*)y, (const __nv_bfloat16*)w_down, (void*)per_slot, order,

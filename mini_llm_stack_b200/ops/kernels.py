@@ -674,9 +674,9 @@ class Ops:
                    "topk": _decl(lib, "mls_route_topk", [_P, _I, _I, _I, _I, _P, _P, _P]),
                    "sort": _decl(lib, "mls_route_sort", [_P, _I, _I, _P, _P, _P, _P, _I, _P, _P]),
                    "glu": _decl(lib, "mls_expert_glu",
-                                [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P]),
+                                [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
                    "down": _decl(lib, "mls_expert_down",
-                                 [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P]),
+                                 [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
                    "combine": _decl(lib, "mls_expert_combine",
                                     [_P, _I, _P, _I, _P, _I, _I, _I, _P])}
         else:
@@ -850,6 +850,13 @@ class Ops:
         rows = int(self._part_lib("experts")["tile_rows"]())
         return (n_slots + rows - 1) // rows + n_experts
 
+    @staticmethod
+    def _many_rows(n_slots: int, n_experts: int) -> int:
+        """Whether an expert has, on average, rows for more than two 32-row tiles: a CTA of
+        the tensor-core kernel then takes four tiles of an expert against one load of its
+        weights (the sums are the same either way)."""
+        return 1 if n_slots >= 64 * n_experts else 0
+
     def expert_glu(self, h, w_gate_up, y, work: dict, top: int, scale_in: bool) -> None:
         """``y[p] = silu(Wg[e] a) * (Wu[e] a)`` for the sorted slots; ``w_gate_up [E, 2F, K]``."""
         n_experts, f2, k = w_gate_up.shape
@@ -861,7 +868,7 @@ class Ops:
             _ptr(h), _ptr(w_gate_up), _ptr(y), _code(h.dtype), _ptr(work["order"]),
             _ptr(work["offsets"]), _ptr(work["tile_expert"]), _ptr(work["tile_row0"]),
             work["max_tiles"], _ptr(work["weight"]), top, 1 if scale_in else 0, f2 // 2, k,
-            self._stream()), "expert_glu")
+            self._many_rows(y.shape[0], n_experts), self._stream()), "expert_glu")
 
     def expert_down(self, y, w_down, per_slot, work: dict, top: int, scale_out: bool) -> None:
         """``per_slot[slot] = Wd[e] y[p]`` (float32); ``w_down [E, D, F]``."""
@@ -874,7 +881,7 @@ class Ops:
             _ptr(y), _ptr(w_down), _ptr(per_slot), _code(y.dtype), _ptr(work["order"]),
             _ptr(work["offsets"]), _ptr(work["tile_expert"]), _ptr(work["tile_row0"]),
             work["max_tiles"], _ptr(work["weight"]), top, 1 if scale_out else 0, d, f,
-            self._stream()), "expert_down")
+            self._many_rows(y.shape[0], n_experts), self._stream()), "expert_down")
 
     def expert_combine(self, per_slot, top: int, shared, delta) -> None:
         """``delta[t] = sum_j per_slot[t * top + j] + shared[t]``."""
