@@ -18,7 +18,7 @@
 
 namespace {
 constexpr int WARPS = 4;
-constexpr int MAX_HD = 256;
+constexpr int MAX_HD = 512;
 
 // q . k over one key row, accumulated in the order i = 0 .. hd-1.
 __device__ __forceinline__ float dot_row(const float* q, const float* k, int hd) {

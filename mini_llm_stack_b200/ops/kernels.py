@@ -477,8 +477,10 @@ class Ops:
 
     def require_attention(self, hd: int, n_heads: int = 0, n_kv: int = 0) -> None:
         """Make sure attention kernels for this head size exist, or say why not."""
-        _need(hd % 16 == 0 and 16 <= hd <= 256,
-              f"attention kernels take head sizes 16..256 in steps of 16, not {hd}")
+        _need(hd % 16 == 0 and 16 <= hd <= 512,
+              f"attention kernels take head sizes 16..512 in steps of 16, not {hd}")
+        if hd > 256:
+            return          # beyond the tensor-core kernels: the one-warp-per-row kernel, both types
         if self.act_dtype == torch.bfloat16 and hd not in self._attention_libs:
             lib = self._load("attention", {"MLS_HEAD_DIM": int(hd)})
             fn = _decl(lib, "mls_attention_mma",
@@ -527,7 +529,8 @@ class Ops:
                 # takes over beyond that)
                 "cluster_splits": 8 if tma and os.environ.get(
                     "MLS_B200_CLUSTER_MERGE", "1") != "0" else 0,
-                "tensor_cores": self.act_dtype == torch.bfloat16 and self.attention_impl != "simt"}
+                "tensor_cores": (self.act_dtype == torch.bfloat16 and self.attention_impl != "simt"
+                                 and hd <= 256)}
 
     def paged_attention(self, qkv, out, cache, step, n_heads: int, n_kv: int, hd: int,
                         scale: float, window: int, plan=None) -> None:
@@ -538,7 +541,7 @@ class Ops:
         t = step.n_tokens
         _need(out.shape == (t, n_heads * hd) and out.is_contiguous(), "attention: bad out")
         _need(cache.k_pool.dtype == qkv.dtype, "attention: cache and activations differ")
-        if qkv.dtype == torch.bfloat16 and self.attention_impl != "simt":
+        if qkv.dtype == torch.bfloat16 and self.attention_impl != "simt" and hd <= 256:
             fns = self._attention_libs.get(hd)
             _need(fns is not None, f"attention kernels for head size {hd} were not required")
             fn, tc = fns

@@ -753,7 +753,7 @@ def test_attention_refuses_head_sizes_it_does_not_have(rts):
     with pytest.raises(KernelError, match="steps of 16"):
         rts[torch.bfloat16].ops.require_attention(40)
     with pytest.raises(KernelError, match="steps of 16"):
-        rts[torch.float32].ops.require_attention(272)
+        rts[torch.float32].ops.require_attention(528)
 
 
 @pytest.mark.parametrize("block, window", [(8, None), (16, None), (32, None), (64, None),

@@ -150,6 +150,18 @@ def test_layernorm_kernel_with_every_addend(rt32):
                               atol=2e-5)
 
 
+def test_residual_add_kernel(rt32):
+    """What a norm of another kind uses to settle a pass's addends."""
+    g = torch.Generator().manual_seed(5)
+    x, rows, vec = torch.randn(7, 52, generator=g), torch.randn(7, 52, generator=g), \
+        torch.randn(52, generator=g)
+    xd = x.cuda()
+    rt32.ops.residual_add(xd, rows.cuda(), vec.cuda())
+    assert torch.allclose(xd.cpu(), x + rows + vec, atol=1e-6)
+    rt32.ops.residual_add(xd, None, vec.cuda().bfloat16())
+    assert torch.allclose(xd.cpu(), x + rows + vec + vec.bfloat16().float(), atol=1e-6)
+
+
 def test_clamped_glu_kernel(rt32):
     g = torch.Generator().manual_seed(1)
     gu = (torch.randn(5, 2 * 37, generator=g) * 3).cuda()
@@ -201,6 +213,9 @@ ONE_LAYER = {
     "latent": {"type": "latent_attention", "mixer": Z.latent(3, 8, 24, 40, 12, 0.6), "mlp": None},
     "latent_one_head": {"type": "latent_attention", "mixer": Z.latent(1, 16, 8, 16, 16, 0.5),
                         "mlp": None},
+    # a latent beyond the tensor-core kernels' head sizes
+    "latent_wide": {"type": "latent_attention", "mixer": Z.latent(2, 16, 24, 300, 40, 0.1),
+                    "mlp": None},
     "mlstm": {"type": "mlstm", "mixer": Z.mlstm(2, 12, 20, 6.0), "mlp": None},
     "mlstm_many_columns": {"type": "mlstm", "mixer": Z.mlstm(1, 40, 150, 20.0), "mlp": None},
     "dense": {"type": "latent_attention", "mixer": Z.latent(1, 8, 8, 16, 8, 0.5),
