@@ -24,3 +24,22 @@ def test_more_than_one_gpu_is_one_line_and_exit_code_two():
     out = _run("--gpus", "2", "--steps", "2", "--warmup", "3")
     assert out.returncode == 2
     assert len(out.stdout.strip().splitlines()) == 1 and "one GPU" in out.stdout
+
+
+def test_design_option_builds_layers_of_equal_size():
+    """The option that sets Zededra layers beside the dense decoder: its configurations
+    parse, and the two arms hold the same width, heads, feed-forward and cache bytes a token."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("design_bench", ROOT / "baseline" / "design_bench.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    from mini_llm_stack_b200.config import config_from_dict
+    assert "--design" in _run("--help").stdout
+    for s in mod.SIZES.values():
+        dense = config_from_dict(mod.llama_config(s, 2))
+        for kind in ("latent_dense", "latent_moe", "mlstm_dense"):
+            z = config_from_dict(mod.zededra_config(s, kind, 2))
+            assert z.width == dense.d_model and len(z.layers) == dense.n_layers
+        latent = mod.zededra_config(s, "latent_dense", 2)["layers"][0]
+        assert latent["mixer"]["heads"] == dense.n_heads and latent["mlp"]["ff"] == dense.intermediate_size
+        assert 2 * dense.n_kv_heads * dense.head_dim >= latent["mixer"]["kv_rank"]
