@@ -370,7 +370,7 @@ def main() -> int:
                     help="decode: the contract's line; the others serve a request mix through "
                          "the scheduler and print their own line")
     ap.add_argument("--design", default=None, choices=["zededra"],
-                    help="instead of the contract's line: layers of this design at sizes that "
+                    help="instead of the default line: layers of this design at sizes that "
                          "resemble a real model's, beside the dense decoder at equal size "
                          "(prefill and decode tokens/s and the time of every kind of kernel)")
     ap.add_argument("--size", default=None, choices=["1b", "8b"],
