@@ -14,7 +14,8 @@ into groups by what they need.  Slots with the same ``PagedKV`` spec share one
 page pool and one block table per request (a page id means the same page in
 every member of the group, as one table serves all layers in the reference);
 a group with a window gives pages back as soon as the window has passed them.
-Slots with a ``FixedState`` spec share the request's state slot.
+Slots with a ``FixedState`` spec share the request's state slot.  A slot whose spec is
+``PagedWithState`` is a member of a paged group and of a fixed group at once.
 
     reserve(req, n)  -> bool   pages for the next n tokens, all groups or none
     commit(req, n)             the n tokens are stored; windows release pages
@@ -29,7 +30,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-from ..parts.base import CacheHandle, FixedState, PagedKV
+from ..parts.base import CacheHandle, FixedState, PagedKV, PagedWithState
 from .page_pool import PagePool
 from .state_slots import StateSlotPool
 
@@ -78,16 +79,12 @@ class CacheManager:
         self.paged: list[PagedGroup] = []
         self.fixed: list[FixedGroup] = []
         self._records: dict = {}
-        self._slot_home: list = []    # cache slot -> ("paged"|"fixed"|"none", gid, member)
+        self._slot_home: list = []
 
         by_key: dict = {}
-        for slot, spec in enumerate(specs):
-            if spec is None:
-                self._slot_home.append(("none", -1, -1))
-                continue
-            kind = "paged" if isinstance(spec, PagedKV) else "fixed"
-            if kind == "fixed" and not isinstance(spec, FixedState):
-                raise CacheError(f"cache slot {slot}: unknown cache spec {spec!r}")
+
+        def join(kind, spec):
+            """(gid, member) of the slot in the group of ``spec``, made if need be."""
             key = (kind, spec)
             if key not in by_key:
                 if kind == "paged":
@@ -99,8 +96,21 @@ class CacheManager:
                     by_key[key] = FixedGroup(len(self.fixed), spec, [], None)
                     self.fixed.append(by_key[key])
             grp = by_key[key]
-            self._slot_home.append((kind, grp.gid, len(grp.members)))
             grp.members.append(slot)
+            return grp.gid, len(grp.members) - 1
+
+        # cache slot -> ((paged gid, member) or None, (fixed gid, member) or None)
+        for slot, spec in enumerate(specs):
+            if spec is None:
+                self._slot_home.append((None, None))
+            elif isinstance(spec, PagedKV):
+                self._slot_home.append((join("paged", spec), None))
+            elif isinstance(spec, FixedState):
+                self._slot_home.append((None, join("fixed", spec)))
+            elif isinstance(spec, PagedWithState):
+                self._slot_home.append((join("paged", spec.paged), join("fixed", spec.state)))
+            else:
+                raise CacheError(f"cache slot {slot}: unknown cache spec {spec!r}")
         if allocate:
             for g in self.paged:
                 # one pool a member where keys and values are the same cached vector
@@ -118,20 +128,20 @@ class CacheManager:
     def handles(self) -> list:
         """One ``CacheHandle`` per cache slot, in slot order."""
         out = []
-        for kind, gid, m in self._slot_home:
-            if kind == "paged":
-                g = self.paged[gid]
-                out.append(CacheHandle(
-                    kind="paged", group=gid,
+        for paged, fixed in self._slot_home:
+            handle = CacheHandle()
+            if fixed is not None:
+                g = self.fixed[fixed[0]]
+                handle = CacheHandle(kind="fixed", group=g.gid,
+                                     state=None if g.state is None else g.state[fixed[1]])
+            if paged is not None:
+                g, m = self.paged[paged[0]], paged[1]
+                handle = CacheHandle(
+                    kind="paged", group=g.gid,
                     k_pool=None if g.kv is None else g.kv[m, 0],
                     v_pool=None if g.kv is None else g.kv[m, g.kv.shape[1] - 1],
-                    window=g.spec.window))
-            elif kind == "fixed":
-                g = self.fixed[gid]
-                out.append(CacheHandle(kind="fixed", group=gid,
-                                       state=None if g.state is None else g.state[m]))
-            else:
-                out.append(CacheHandle())
+                    window=g.spec.window, state=handle.state)
+            out.append(handle)
         return out
 
     # --------------------------------------------------------------- accounting
@@ -359,9 +369,9 @@ class CacheManager:
     def gather_contiguous(self, slot: int, owner, n: int | None = None):
         """K and V of one cache slot for ``owner`` as [Hkv, n, hd]
         (serve/kv_cache.py:124-135); positions a window released read as NaN."""
-        kind, gid, m = self._slot_home[slot]
-        if kind != "paged":
+        if self._slot_home[slot][0] is None:
             raise CacheError("gather_contiguous needs a paged cache slot")
+        gid, m = self._slot_home[slot][0]
         g = self.paged[gid]
         rec = self._records[owner]
         n = rec.length if n is None else n

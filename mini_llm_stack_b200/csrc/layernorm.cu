@@ -78,7 +78,45 @@ __global__ void residual_add_kernel(float* __restrict__ x, const float* __restri
         x[i] = v;
     }
 }
+
+// x += delta (a tensor, the parts of a product cut along K, or nothing); then
+// out[t] = [x[t] | other[t]] in the activation type: the input of a projection that reads
+// the stream beside a second stream.
+__global__ void settle_concat_kernel(float* __restrict__ x, const void* __restrict__ delta,
+                                     int delta_dtype, int n_parts, size_t part_stride,
+                                     const float* __restrict__ other, void* __restrict__ out,
+                                     int out_dtype, size_t n, int d) {
+    chain_release();
+    chain_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x) {
+        float v = x[i];
+        if (delta) {
+            float add = 0.f;
+            for (int k = 0; k < n_parts; ++k)
+                add += load_as_float(delta, i + (size_t)k * part_stride, delta_dtype);
+            v += add;
+            x[i] = v;
+        }
+        const size_t t = i / d, c = i - t * d;
+        store_from_float(out, t * 2 * d + c, out_dtype, v);
+        store_from_float(out, t * 2 * d + d + c, out_dtype, other[i]);
+    }
+}
 }  // namespace
+
+MLS_API int mls_settle_concat(float* x, const void* delta, int delta_dtype, int delta_parts,
+                              long long part_stride, const float* other, void* out,
+                              int out_dtype, int n_rows, int d, cudaStream_t stream) {
+    if (n_rows <= 0 || d <= 0) return 0;
+    const size_t n = (size_t)n_rows * d;
+    const int blocks = (int)((n + 255) / 256 < (size_t)(8 * sm_count()) ? (n + 255) / 256
+                                                                       : 8 * sm_count());
+    MLS_LAUNCH((settle_concat_kernel), dim3(blocks), dim3(256), 0, stream, x, delta, delta_dtype,
+               delta_parts < 1 ? 1 : delta_parts, (size_t)part_stride, other, out, out_dtype, n,
+               d);
+    return launch_status();
+}
 
 MLS_API int mls_add_layernorm(float* x, const void* delta, int delta_dtype, int delta_parts,
                               long long part_stride, const float* more_rows, const void* more_vec,

@@ -1,0 +1,265 @@
+// Short causal convolutions over time whose last inputs are carried per request, and
+// what a mixer does right around them.
+//
+// A convolution of `taps` taps on a channel, y_t = sum_j w[j] * u_(t - taps + 1 + j) with
+// zeros before the sequence's start, needs the taps - 1 inputs before a step's first
+// token.  They live in the request's state slot as a tail [taps - 1, channels] of
+// float32, oldest first, zero when the slot is claimed (so a tail that reaches before the
+// start reads as zeros without a test).  A step reads the tail in the kernel that
+// convolves and moves it on in mls_tail_update, a launch of its own, so that no block
+// reads what another writes.  "The previous token's row" (a token shift) is the tail of
+// a two-tap convolution.
+//
+//   mls_qk_conv_norm_rope_store   q|k projection (float32) + bias -> convolution ->
+//       v := the convolved k (stored in the value pages) -> RMS norm over the whole q
+//       row and over the whole k row -> rotation of the first `dims` entries of every
+//       head, entry 2i paired with 2i + 1 -> q into the attention's row, k into the pages
+//   mls_token_shift_mix           mix_s = h + (h_prev - h) * mu_s for several s at once
+//   mls_tail_update               tail := the last taps - 1 inputs after this step
+//
+// Angles are formed in float64 (position * frequency, frequencies handed over as
+// float64) and their cosine and sine rounded once to float32; sums, norms and the
+// rotation are float32.
+#include "common.cuh"
+#include "page_tail.cuh"
+
+namespace {
+constexpr int SC_THREADS = 256;
+
+// u_(i) of channel c for the step index i of request rows [row0, ...): from the step's
+// rows if i >= 0, else from the tail (i = -1 is the newest tail row).
+__device__ __forceinline__ float conv_input(const float* __restrict__ proj, int width, int col,
+                                            const void* __restrict__ bias, int w_dtype,
+                                            const float* __restrict__ tail, int n_tail,
+                                            int channels, int c, int row0, int i) {
+    if (i >= 0) {
+        float v = proj[(size_t)(row0 + i) * width + col];
+        if (bias) v += load_as_float(bias, c, w_dtype);
+        return v;
+    }
+    return tail[(size_t)(n_tail + i) * channels + c];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SC_THREADS)
+qk_conv_norm_rope_store_kernel(
+        const float* __restrict__ proj, const void* __restrict__ bias,
+        const void* __restrict__ conv_w, int taps, const void* __restrict__ q_norm,
+        const void* __restrict__ k_norm, int w_dtype, float eps,
+        const float* __restrict__ tail, long long tail_stride,
+        const int* __restrict__ state_slot, const int* __restrict__ cu_q,
+        const int* __restrict__ req_of_token, const int* __restrict__ positions,
+        const double* __restrict__ freq, int rot_dims,
+        T* __restrict__ q_out, int q_row, const int* __restrict__ slot_map,
+        T* __restrict__ k_pool, T* __restrict__ v_pool, int block_size, long long pool_slots,
+        int n_tokens, int n_heads, int n_kv, int hd, int writes, int* status) {
+    chain_release();
+    extern __shared__ float smem[];
+    const int cq = n_heads * hd, ck = n_kv * hd, channels = cq + ck;
+    float* y = smem;                       // [channels] convolved, then normalised
+    float* cs = y + channels;              // [rot_dims]: cos | sin
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const int slot = writes ? slot_map[t] : -1;
+    const int rest = writes ? page_tail_to_clear(slot_map, t, n_tokens, slot, block_size) : 0;
+    chain_wait();
+    const int r = req_of_token[t], row0 = cu_q[r], i_t = t - row0, p = positions[t];
+    const int n_tail = taps - 1;
+    const float* my_tail = n_tail > 0 ? tail + (size_t)state_slot[r] * tail_stride : nullptr;
+    if (threadIdx.x < rot_dims / 2) {
+        double s, c;
+        sincos((double)p * freq[threadIdx.x], &s, &c);
+        cs[threadIdx.x] = (float)c;
+        cs[rot_dims / 2 + threadIdx.x] = (float)s;
+    }
+    float ssq = 0.f, ssk = 0.f;
+    for (int c = threadIdx.x; c < channels; c += SC_THREADS) {
+        float acc;
+        if (n_tail > 0) {
+            acc = 0.f;
+            for (int j = 0; j < taps; ++j)
+                acc = fmaf(load_as_float(conv_w, (size_t)c * taps + j, w_dtype),
+                           conv_input(proj, channels, c, bias, w_dtype, my_tail, n_tail, channels,
+                                      c, row0, i_t - n_tail + j), acc);
+        } else {
+            acc = conv_input(proj, channels, c, bias, w_dtype, nullptr, 0, channels, c, row0, i_t);
+            if (taps == 1) acc *= load_as_float(conv_w, c, w_dtype);
+        }
+        y[c] = acc;
+        if (c < cq) ssq = fmaf(acc, acc, ssq); else ssk = fmaf(acc, acc, ssk);
+    }
+    const bool slot_ok = slot >= 0 && slot < pool_slots;
+    if (writes && !slot_ok && threadIdx.x == 0) atomicOr(status, MLS_STATUS_BAD_SLOT);
+    const float inv_q = 1.0f / sqrtf(block_sum(ssq, scratch) / (float)cq + eps);
+    const float inv_k = 1.0f / sqrtf(block_sum(ssk, scratch) / (float)ck + eps);
+    // (block_sum's barriers also make y and cs visible to every thread)
+    const long long page = slot_ok ? slot / block_size : 0;
+    const int off = slot_ok ? slot % block_size : 0;
+    const long long n_pages = pool_slots / block_size;
+    // values: the convolved keys as they are
+    if (writes && slot_ok)
+        for (int c = threadIdx.x; c < ck; c += SC_THREADS) {
+            const int g = c / hd, e = c - g * hd;
+            Elem<T>::store(v_pool + (((size_t)g * n_pages + page) * block_size + off) * hd + e,
+                           y[cq + c]);
+        }
+    // queries and keys: norm, then the rotation of pairs (2i, 2i + 1) below rot_dims
+    for (int c = threadIdx.x; c < channels; c += SC_THREADS) {
+        const bool is_q = c < cq;
+        const int cc = is_q ? c : c - cq;
+        const int e = cc % hd;
+        const void* nw = is_q ? q_norm : k_norm;
+        const float inv = is_q ? inv_q : inv_k;
+        float v = y[c] * inv * load_as_float(nw, cc, w_dtype);
+        if (e < rot_dims) {
+            const int mate = (e & 1) ? c - 1 : c + 1, mcc = (e & 1) ? cc - 1 : cc + 1;
+            const float m = y[mate] * inv * load_as_float(nw, mcc, w_dtype);
+            const float co = cs[e >> 1], si = cs[rot_dims / 2 + (e >> 1)];
+            // even entry: a cos - b sin; odd entry: b cos + a sin
+            v = (e & 1) ? __fadd_rn(__fmul_rn(v, co), __fmul_rn(m, si))
+                        : __fsub_rn(__fmul_rn(v, co), __fmul_rn(m, si));
+        }
+        if (is_q) {
+            Elem<T>::store(q_out + (size_t)t * q_row + c, v);
+        } else if (writes && slot_ok) {
+            const int g = cc / hd;
+            Elem<T>::store(k_pool + (((size_t)g * n_pages + page) * block_size + off) * hd + e, v);
+        }
+    }
+    if (writes && slot_ok)
+        clear_page_tail<T>(rest, slot, block_size, (int)n_pages, n_kv, hd, k_pool, v_pool);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SC_THREADS)
+token_shift_mix_kernel(const T* __restrict__ h, const void* __restrict__ mu, int w_dtype,
+                       int n_mix, const float* __restrict__ tail, long long tail_stride,
+                       const int* __restrict__ state_slot, const int* __restrict__ cu_q,
+                       const int* __restrict__ req_of_token, T* __restrict__ out,
+                       float* __restrict__ out_f32, int n_tokens, int d) {
+    chain_release();
+    chain_wait();
+    const int t = blockIdx.x;
+    const int r = req_of_token[t];
+    const bool first = t == cu_q[r];
+    const float* prev_tail = tail + (size_t)state_slot[r] * tail_stride;
+    for (int c = threadIdx.x; c < d; c += SC_THREADS) {
+        const float cur = Elem<T>::load(h + (size_t)t * d + c);
+        const float prev = first ? prev_tail[c] : Elem<T>::load(h + (size_t)(t - 1) * d + c);
+        const float diff = prev - cur;
+        for (int s = 0; s < n_mix; ++s) {
+            const float v = fmaf(diff, load_as_float(mu, (size_t)s * d + c, w_dtype), cur);
+            // the last mix may be wanted in float32 (it feeds a float32 product)
+            if (s == n_mix - 1 && out_f32) out_f32[(size_t)t * d + c] = v;
+            else Elem<T>::store(out + ((size_t)s * n_tokens + t) * d + c, v);
+        }
+    }
+}
+
+// One thread a channel walks the tail's rows oldest first: row j becomes the input
+// n_tail - j places before the end of the sequence as it is after this step, which is a
+// row of this step or, for a short step, the old tail's row j + n (read before that row
+// is written, since j + n > j).
+template <typename T>
+__global__ void __launch_bounds__(SC_THREADS)
+tail_update_kernel(const T* __restrict__ src, int width, int col0, const void* __restrict__ bias,
+                   int w_dtype, float* __restrict__ tail, long long tail_stride, int n_tail,
+                   int channels, const int* __restrict__ state_slot,
+                   const int* __restrict__ cu_q) {
+    chain_release();
+    chain_wait();
+    const int r = blockIdx.y;
+    const int row0 = cu_q[r], n = cu_q[r + 1] - row0;
+    if (n <= 0) return;
+    float* my = tail + (size_t)state_slot[r] * tail_stride;
+    const int c = blockIdx.x * SC_THREADS + threadIdx.x;
+    if (c >= channels) return;
+    for (int j = 0; j < n_tail; ++j) {
+        const int i = n - n_tail + j;
+        float v;
+        if (i >= 0) {
+            v = Elem<T>::load(src + (size_t)(row0 + i) * width + col0 + c);
+            if (bias) v += load_as_float(bias, c, w_dtype);
+        } else {
+            v = my[(size_t)(j + n) * channels + c];
+        }
+        my[(size_t)j * channels + c] = v;
+    }
+}
+}  // namespace
+
+MLS_API int mls_qk_conv_norm_rope_store(
+        const float* proj, const void* bias, const void* conv_w, int taps, const void* q_norm,
+        const void* k_norm, int w_dtype, float eps, const float* tail, long long tail_stride,
+        const int* state_slot, const int* cu_q, const int* req_of_token, const int* positions,
+        const double* freq, int rot_dims, void* q_out, int q_row, int act_dtype,
+        const int* slot_map, void* k_pool, void* v_pool, int block_size, long long pool_slots,
+        int n_tokens, int n_heads, int n_kv, int hd, int writes, int* status,
+        cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (taps < 0 || (taps > 1 && !tail) || rot_dims < 0 || rot_dims > hd || (rot_dims & 1) ||
+        rot_dims / 2 > SC_THREADS || (rot_dims > 0 && !freq))
+        return MLS_ERR_UNSUPPORTED;
+    const size_t smem = ((size_t)(n_heads + n_kv) * hd + rot_dims) * sizeof(float);
+    if (smem > 200 * 1024) return MLS_ERR_UNSUPPORTED;
+    if (act_dtype == MLS_BF16) {
+        auto kernel = qk_conv_norm_rope_store_kernel<__nv_bfloat16>;
+        if (smem > 48 * 1024) {
+            const int rc = (int)cudaFuncSetAttribute(
+                kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (rc) return rc;
+        }
+        MLS_LAUNCH(kernel, dim3(n_tokens), dim3(SC_THREADS), smem, stream, proj, bias, conv_w,
+                   taps, q_norm, k_norm, w_dtype, eps, tail, tail_stride, state_slot, cu_q,
+                   req_of_token, positions, freq, rot_dims, (__nv_bfloat16*)q_out, q_row, slot_map,
+                   (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, block_size, pool_slots,
+                   n_tokens, n_heads, n_kv, hd, writes, status);
+    } else {
+        auto kernel = qk_conv_norm_rope_store_kernel<float>;
+        if (smem > 48 * 1024) {
+            const int rc = (int)cudaFuncSetAttribute(
+                kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (rc) return rc;
+        }
+        MLS_LAUNCH(kernel, dim3(n_tokens), dim3(SC_THREADS), smem, stream, proj, bias, conv_w,
+                   taps, q_norm, k_norm, w_dtype, eps, tail, tail_stride, state_slot, cu_q,
+                   req_of_token, positions, freq, rot_dims, (float*)q_out, q_row, slot_map,
+                   (float*)k_pool, (float*)v_pool, block_size, pool_slots, n_tokens, n_heads,
+                   n_kv, hd, writes, status);
+    }
+    return launch_status();
+}
+
+MLS_API int mls_token_shift_mix(const void* h, int act_dtype, const void* mu, int w_dtype,
+                                int n_mix, const float* tail, long long tail_stride,
+                                const int* state_slot, const int* cu_q, const int* req_of_token,
+                                void* out, float* out_f32, int n_tokens, int d,
+                                cudaStream_t stream) {
+    if (n_tokens <= 0 || n_mix <= 0) return 0;
+    if (act_dtype == MLS_BF16)
+        MLS_LAUNCH((token_shift_mix_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(SC_THREADS), 0,
+                   stream, (const __nv_bfloat16*)h, mu, w_dtype, n_mix, tail, tail_stride,
+                   state_slot, cu_q, req_of_token, (__nv_bfloat16*)out, out_f32, n_tokens, d);
+    else
+        MLS_LAUNCH((token_shift_mix_kernel<float>), dim3(n_tokens), dim3(SC_THREADS), 0, stream,
+                   (const float*)h, mu, w_dtype, n_mix, tail, tail_stride, state_slot, cu_q,
+                   req_of_token, (float*)out, out_f32, n_tokens, d);
+    return launch_status();
+}
+
+MLS_API int mls_tail_update(const void* src, int src_dtype, int width, int col0, const void* bias,
+                            int w_dtype, float* tail, long long tail_stride, int n_tail,
+                            int channels, const int* state_slot, const int* cu_q,
+                            int n_requests, cudaStream_t stream) {
+    if (n_requests <= 0 || n_tail <= 0 || channels <= 0) return 0;
+    const dim3 grid((channels + SC_THREADS - 1) / SC_THREADS, n_requests);
+    if (src_dtype == MLS_BF16)
+        MLS_LAUNCH((tail_update_kernel<__nv_bfloat16>), grid, dim3(SC_THREADS), 0, stream,
+                   (const __nv_bfloat16*)src, width, col0, bias, w_dtype, tail, tail_stride,
+                   n_tail, channels, state_slot, cu_q);
+    else
+        MLS_LAUNCH((tail_update_kernel<float>), grid, dim3(SC_THREADS), 0, stream,
+                   (const float*)src, width, col0, bias, w_dtype, tail, tail_stride, n_tail,
+                   channels, state_slot, cu_q);
+    return launch_status();
+}

@@ -81,7 +81,54 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out
                    clamped_glu(Elem<T>::load(row + i), Elem<T>::load(row + inter + i), alpha,
                                limit));
 }
+
+// Activations without a gate: out = act(in), element by element (in place allowed).
+// kind 0: the square of relu.
+template <typename T>
+__global__ void unary_act_kernel(const T* __restrict__ in, T* __restrict__ out, size_t n,
+                                 int kind) {
+    chain_release();
+    chain_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x) {
+        const float z = fmaxf(Elem<T>::load(in + i), 0.f);
+        Elem<T>::store(out + i, z * z);
+    }
+}
+
+__global__ void scale_f32_kernel(float* __restrict__ x, size_t n, float scale) {
+    chain_release();
+    chain_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x)
+        x[i] *= scale;
+}
 }  // namespace
+
+// out[i] = relu(in[i])^2 (kind 0; other kinds are refused).
+MLS_API int mls_unary_act(const void* in, void* out, int dtype, long long n, int kind,
+                          cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (kind != 0) return MLS_ERR_UNSUPPORTED;
+    const long long want = (n + 255) / 256;
+    const int blocks = (int)(want < 16LL * sm_count() ? want : 16LL * sm_count());
+    if (dtype == MLS_BF16)
+        MLS_LAUNCH((unary_act_kernel<__nv_bfloat16>), dim3(blocks), dim3(256), 0, stream,
+                   (const __nv_bfloat16*)in, (__nv_bfloat16*)out, (size_t)n, kind);
+    else
+        MLS_LAUNCH((unary_act_kernel<float>), dim3(blocks), dim3(256), 0, stream,
+                   (const float*)in, (float*)out, (size_t)n, kind);
+    return launch_status();
+}
+
+// x[i] *= scale on float32 values (logits times a constant).
+MLS_API int mls_scale_f32(float* x, long long n, float scale, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    const long long want = (n + 255) / 256;
+    const int blocks = (int)(want < 16LL * sm_count() ? want : 16LL * sm_count());
+    MLS_LAUNCH((scale_f32_kernel), dim3(blocks), dim3(256), 0, stream, x, (size_t)n, scale);
+    return launch_status();
+}
 
 // gu: [T, 2*I], a row holds [gate | up]; out[t, i] = clamped_glu(gate, up).
 MLS_API int mls_clamped_glu(const void* gu, void* out, int dtype, int n_tokens, int inter,

@@ -21,7 +21,7 @@ import torch
 from ..cache.manager import CacheError, CacheManager
 from ..config.registry import build_model, config_from_folder
 from ..ops.kernels import Runtime
-from ..weights.loader import device_dtype, load_tensors
+from ..weights.loader import device_dtype, load_tensors, open_weights
 from ..weights.random_init import random_tensors
 from .batch import BatchBuilder
 
@@ -31,6 +31,10 @@ _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 def load_model(folder, dtype: str | None = None, device="cuda:0"):
     """Model of a folder (config.json + model.safetensors), bound to a runtime."""
     config = config_from_folder(folder)
+    if hasattr(config, "with_tensor_shapes"):
+        # a design may leave sizes to its tensors' shapes: the file's header has them
+        with open_weights(folder) as f:
+            config = config.with_tensor_shapes({n: tuple(e.shape) for n, e in f.entries.items()})
     run_dtype = _TORCH_DTYPES[dtype or config.dtype]
     runtime = Runtime(device, run_dtype)
     model = build_model(config)

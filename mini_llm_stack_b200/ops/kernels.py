@@ -123,7 +123,7 @@ class Ops:
         self._libs: list = []                    # every kernel library in use
         self._chained = True                     # what the libraries were last told
         core = self._load("core")
-        self._embed = _decl(core, "mls_embed", [_P, _P, _I, _P, _I, _I, _I, _P, _P])
+        self._embed = _decl(core, "mls_embed", [_P, _P, _I, _P, _I, _I, _I, _F, _P, _P])
         self._add_rmsnorm = _decl(core, "mls_add_rmsnorm",
                                   [_P, _P, _I, _P, _I, _F, _P, _I, _I, _I, _P, _I, _LL, _P, _P])
         self._gemm_f32 = _decl(core, "mls_gemm_f32", [_P, _P, _P, _I, _I, _I, _P])
@@ -132,9 +132,11 @@ class Ops:
                                   _LL, _I, _P, _I, _LL, _P, _P])
         self._attention_simt = _decl(core, "mls_attention_simt",
                                      [_P, _P, _I, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I,
-                                      _I, _F, _I, _LL, _P])
+                                      _I, _F, _I, _F, _LL, _P])
         self._swiglu = _decl(core, "mls_swiglu", [_P, _P, _I, _I, _I, _P])
         self._clamped_glu = _decl(core, "mls_clamped_glu", [_P, _P, _I, _I, _I, _F, _F, _P])
+        self._unary_act = _decl(core, "mls_unary_act", [_P, _P, _I, _LL, _I, _P])
+        self._scale_f32 = _decl(core, "mls_scale_f32", [_P, _LL, _F, _P])
         self._part_libs: dict = {}               # kernels of parts only some models have
         self._sample = _decl(core, "mls_sample", [_P, _P, _P, _P, _I, _I, _P, _P])
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -211,14 +213,14 @@ class Ops:
                                                                 f"status {code}"))
 
     # ------------------------------------------------------------------ kernels
-    def embed(self, token_ids, table, x, vocab: int) -> None:
+    def embed(self, token_ids, table, x, vocab: int, scale: float = 1.0) -> None:
         t, d = x.shape
         _need(x.dtype == torch.float32 and x.is_contiguous(), "embed: x must be float32")
         _need(table.shape == (vocab, d) and table.is_contiguous(), "embed: bad table")
         _need(token_ids.dtype == torch.int32 and token_ids.numel() >= t, "embed: bad ids")
         self.launches += 1
         _check(self._embed(_ptr(token_ids), _ptr(table), _code(table.dtype), _ptr(x), t, d,
-                           vocab, _ptr(self.status), self._stream()), "embed")
+                           vocab, float(scale), _ptr(self.status), self._stream()), "embed")
 
     def _delta_args(self, delta, t: int, d: int, what: str):
         """(pointer, type code, parts, part stride) of a pending residual delta."""
@@ -510,7 +512,13 @@ class Ops:
         fn = _decl(lib, "mls_attention_tc_set_rows", [_I], restype=None)
         fn(rows)
 
-    def attention_facts(self, hd: int) -> dict:
+    def attention_tensor_cores(self, hd: int, softcap: float = 0.0) -> bool:
+        """Whether the tensor-core attention kernels take this step's attention (else
+        the one-warp-per-row kernel does, which takes every size and option)."""
+        return (self.act_dtype == torch.bfloat16 and self.attention_impl != "simt"
+                and hd <= 256 and not softcap)
+
+    def attention_facts(self, hd: int, softcap: float = 0.0) -> dict:
         """What a mixer needs to know of the attention kernels to plan a step's
         launches: ``small_rows`` (requests whose (token, head) rows of one kv head are
         at most this many go to the context-split kernel), ``tile_rows`` and
@@ -529,19 +537,19 @@ class Ops:
                 # takes over beyond that)
                 "cluster_splits": 8 if tma and os.environ.get(
                     "MLS_B200_CLUSTER_MERGE", "1") != "0" else 0,
-                "tensor_cores": (self.act_dtype == torch.bfloat16 and self.attention_impl != "simt"
-                                 and hd <= 256)}
+                "tensor_cores": self.attention_tensor_cores(hd, softcap)}
 
     def paged_attention(self, qkv, out, cache, step, n_heads: int, n_kv: int, hd: int,
-                        scale: float, window: int, plan=None) -> None:
-        """Attention of the step's tokens over the pages.  ``plan`` (the mixer's, from
+                        scale: float, window: int, plan=None, softcap: float = 0.0) -> None:
+        """Attention of the step's tokens over the pages.  ``softcap`` c > 0: scores become
+        ``c * tanh(score / c)`` before the softmax.  ``plan`` (the mixer's, from
         ``attention_facts``): ``n_tiles`` / ``n_tiles_tc`` / ``n_tiles_tc_wide`` tiles of the
         requests that are not small, ``any_small``, ``n_split`` context splits for the small ones."""
         g = step.groups[cache.group]
         t = step.n_tokens
         _need(out.shape == (t, n_heads * hd) and out.is_contiguous(), "attention: bad out")
         _need(cache.k_pool.dtype == qkv.dtype, "attention: cache and activations differ")
-        if qkv.dtype == torch.bfloat16 and self.attention_impl != "simt" and hd <= 256:
+        if self.attention_tensor_cores(hd, softcap) and qkv.dtype == torch.bfloat16:
             fns = self._attention_libs.get(hd)
             _need(fns is not None, f"attention kernels for head size {hd} were not required")
             fn, tc = fns
@@ -583,7 +591,7 @@ class Ops:
         _check(self._attention_simt(
             _ptr(qkv), _ptr(out), _code(qkv.dtype), _ptr(cache.k_pool), _ptr(cache.v_pool),
             _ptr(g.block_table), g.max_blocks, _ptr(step.positions), _ptr(step.req_of_token),
-            t, n_heads, n_kv, hd, g.block_size, float(scale), int(window),
+            t, n_heads, n_kv, hd, g.block_size, float(scale), int(window), float(softcap),
             cache.k_pool.shape[1], self._stream()), "attention_simt")
 
     def _split_launches(self, n_split: int, tma: bool, n_ctas: int) -> int:
@@ -647,6 +655,20 @@ class Ops:
         _check(self._swiglu(_ptr(gu), _ptr(out), _code(out.dtype), t, inter, self._stream()),
                "swiglu")
 
+    def relu_squared(self, z, out) -> None:
+        """``out = relu(z)^2`` element by element (``out`` may be ``z``)."""
+        _need(z.shape == out.shape and z.dtype == out.dtype and z.is_contiguous()
+              and out.is_contiguous(), "relu_squared: operands")
+        self.launches += 1
+        _check(self._unary_act(_ptr(z), _ptr(out), _code(z.dtype), z.numel(), 0, self._stream()),
+               "relu_squared")
+
+    def scale_(self, x, scale: float) -> None:
+        """``x *= scale`` on float32 values."""
+        _need(x.dtype == torch.float32 and x.is_contiguous(), "scale_: float32 values")
+        self.launches += 1
+        _check(self._scale_f32(_ptr(x), x.numel(), float(scale), self._stream()), "scale_")
+
     # ------------------------------------------- parts only some architectures have
     def _part_lib(self, name: str):
         """The kernels of a kind of part, built and loaded when a model first needs them."""
@@ -658,7 +680,9 @@ class Ops:
             fns = {"add_layernorm": _decl(lib, "mls_add_layernorm",
                                           [_P, _P, _I, _I, _LL, _P, _P, _I, _P, _I, _F, _P, _I,
                                            _I, _I, _P, _P]),
-                   "residual_add": _decl(lib, "mls_residual_add", [_P, _P, _P, _I, _I, _I, _P])}
+                   "residual_add": _decl(lib, "mls_residual_add", [_P, _P, _P, _I, _I, _I, _P]),
+                   "settle_concat": _decl(lib, "mls_settle_concat",
+                                          [_P, _P, _I, _I, _LL, _P, _P, _I, _I, _I, _P])}
         elif name == "latent":
             fns = {"norm_store": _decl(lib, "mls_latent_norm_store",
                                        [_P, _I, _I, _I, _I, _P, _P, _I, _F, _P, _I, _P, _P, _I,
@@ -682,6 +706,24 @@ class Ops:
                                  [_P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _P]),
                    "combine": _decl(lib, "mls_expert_combine",
                                     [_P, _I, _P, _I, _P, _I, _I, _I, _P])}
+        elif name == "shortconv":
+            fns = {"qk": _decl(lib, "mls_qk_conv_norm_rope_store",
+                               [_P, _P, _P, _I, _P, _P, _I, _F, _P, _LL, _P, _P, _P, _P, _P, _I,
+                                _P, _I, _I, _P, _P, _P, _I, _LL, _I, _I, _I, _I, _I, _P, _P]),
+                   "shift_mix": _decl(lib, "mls_token_shift_mix",
+                                      [_P, _I, _P, _I, _I, _P, _LL, _P, _P, _P, _P, _P, _I, _I, _P]),
+                   "tail": _decl(lib, "mls_tail_update",
+                                 [_P, _I, _I, _I, _P, _I, _P, _LL, _I, _I, _P, _P, _I, _P])}
+        elif name == "scan":
+            fns = {"scan": _decl(lib, "mls_linear_scan",
+                                 [_P, _I, _I, _I, _P, _I, _I, _I, _P, _I, _I, _I, _P, _I, _P, _P,
+                                  _I, _I, _P, _P, _P, _LL, _I, _I, _I, _I, _P, _P]),
+                   "finish": _decl(lib, "mls_scan_finish",
+                                   [_P, _P, _I, _I, _I, _P, _I, _F, _P, _I, _I, _I, _P]),
+                   "rotate": _decl(lib, "mls_rotate_rows",
+                                   [_P, _I, _I, _I, _I, _P, _P, _I, _F, _P, _I, _I, _I, _P]),
+                   "decay": _decl(lib, "mls_decay_lowrank",
+                                  [_P, _I, _P, _P, _I, _P, _I, _I, _P])}
         else:
             raise KernelError(f"no kernels of a part called {name!r}")
         self._part_libs[name] = fns
@@ -896,6 +938,177 @@ class Ops:
         _check(self._part_lib("experts")["combine"](
             _ptr(per_slot), top, _ptr(shared), _code(shared.dtype) if shared is not None else 0,
             _ptr(delta), _code(delta.dtype), t, d, self._stream()), "expert_combine")
+
+    def settle_concat(self, x, delta, other, out) -> None:
+        """``x += delta`` (a tensor, ``SplitParts`` or None), then ``out[t] = [x[t] | other[t]]``
+        in ``out``'s type."""
+        t, d = x.shape
+        _need(x.dtype == torch.float32 and x.is_contiguous() and other.shape == (t, d)
+              and other.dtype == torch.float32 and other.is_contiguous()
+              and out.shape == (t, 2 * d) and out.is_contiguous(), "settle_concat: operands")
+        dp, dcode, parts, stride = self._delta_args(delta, t, d, "settle_concat")
+        self.launches += 1
+        _check(self._part_lib("layernorm")["settle_concat"](
+            _ptr(x), dp, dcode, parts, stride, _ptr(other), _ptr(out), _code(out.dtype), t, d,
+            self._stream()), "settle_concat")
+        if isinstance(delta, SplitParts):
+            delta.release()
+
+    def qk_conv_norm_rope_store(self, proj, bias, conv_w, taps: int, q_norm, k_norm, eps: float,
+                                tail, freq, rot_dims: int, q_out, cache, step, n_heads: int,
+                                n_kv: int, hd: int) -> None:
+        """From the float32 projection ``proj [T, (H + G) * hd]`` (q heads, then k heads):
+        add ``bias``, convolve every channel over time (``conv_w [C, taps]``; the inputs
+        before the step come from ``tail [slots, (taps - 1) * C]``), store the convolved k
+        as the values, RMS-normalise the whole q row and the whole k row, rotate the first
+        ``rot_dims`` entries of every head (2i with 2i + 1, ``freq`` float64), write q into
+        ``q_out`` and k into the pages.  ``mls_tail_update`` moves the tail on afterwards."""
+        g = step.groups[cache.group]
+        t = step.n_tokens
+        c = (n_heads + n_kv) * hd
+        pool = cache.k_pool
+        _need(proj.shape == (t, c) and proj.dtype == torch.float32 and proj.is_contiguous(),
+              "qk_conv_norm_rope_store: bad projection")
+        _need(pool.is_contiguous() and cache.v_pool.is_contiguous() and pool.shape[0] == n_kv
+              and pool.shape[3] == hd and q_out.dtype == pool.dtype and q_out.is_contiguous()
+              and q_out.shape[0] >= t and q_out.shape[1] >= n_heads * hd,
+              "qk_conv_norm_rope_store: bad pool or output")
+        _need(q_norm.shape == (n_heads * hd,) and k_norm.shape == (n_kv * hd,)
+              and q_norm.dtype == k_norm.dtype, "qk_conv_norm_rope_store: bad norm weights")
+        _need(bias is None or (bias.shape == (c,) and bias.dtype == q_norm.dtype
+                               and bias.is_contiguous()), "qk_conv_norm_rope_store: bad bias")
+        _need(taps == 0 or (conv_w.shape == (c, taps) and conv_w.dtype == q_norm.dtype
+                            and conv_w.is_contiguous()), "qk_conv_norm_rope_store: bad taps")
+        _need(taps <= 1 or (tail.dtype == torch.float32 and tail.stride(1) == 1
+                            and tail.shape[1] == (taps - 1) * c),
+              "qk_conv_norm_rope_store: bad tail")
+        _need(rot_dims == 0 or (freq.dtype == torch.float64 and freq.numel() == rot_dims // 2),
+              "qk_conv_norm_rope_store: bad frequencies")
+        self.launches += 1
+        _check(self._part_lib("shortconv")["qk"](
+            _ptr(proj), _ptr(bias), _ptr(conv_w) if taps else None, taps, _ptr(q_norm),
+            _ptr(k_norm), _code(q_norm.dtype), float(eps), _ptr(tail) if taps > 1 else None,
+            tail.stride(0) if taps > 1 else 0, _ptr(step.state_slot), _ptr(step.cu_q),
+            _ptr(step.req_of_token), _ptr(step.positions), _ptr(freq) if rot_dims else None,
+            rot_dims, _ptr(q_out), q_out.shape[1], _code(pool.dtype), _ptr(g.slot_map), _ptr(pool),
+            _ptr(cache.v_pool), g.block_size, pool.shape[1] * pool.shape[2], t, n_heads, n_kv, hd,
+            1 if cache.writes else 0, _ptr(self.status), self._stream()),
+            "qk_conv_norm_rope_store")
+
+    def tail_update(self, src, col0: int, channels: int, bias, tail, n_tail: int, step) -> None:
+        """``tail [slots, n_tail * channels]`` (float32, oldest row first) becomes the last
+        ``n_tail`` rows of every request's sequence after this step: rows of ``src[:, col0 :
+        col0 + channels]`` (plus ``bias``), or, for a short step, the old tail's."""
+        _need(src.is_contiguous() and src.shape[0] >= step.n_tokens
+              and src.shape[1] >= col0 + channels, "tail_update: bad rows")
+        _need(tail.dtype == torch.float32 and tail.stride(1) == 1
+              and tail.shape[1] == n_tail * channels, "tail_update: bad tail")
+        _need(bias is None or (bias.shape == (channels,) and bias.is_contiguous()),
+              "tail_update: bad bias")
+        self.launches += 1
+        _check(self._part_lib("shortconv")["tail"](
+            _ptr(src), _code(src.dtype), src.shape[1], col0, _ptr(bias),
+            _code(bias.dtype) if bias is not None else 0, _ptr(tail), tail.stride(0), n_tail,
+            channels, _ptr(step.state_slot), _ptr(step.cu_q), step.n_requests, self._stream()),
+            "tail_update")
+
+    def token_shift_mix(self, h, mu, prev, out, out_f32, step) -> None:
+        """``mix_s[t] = h[t] + (h[t - 1] - h[t]) * mu[s]`` for every row s of ``mu [n, d]``,
+        with a request's row before its first of the step from ``prev [slots, d]``
+        (float32).  ``out [n or n - 1, T, d]``; with ``out_f32 [T, d]`` the last mix goes
+        there in float32."""
+        t, d = h.shape
+        n = mu.shape[0]
+        _need(h.is_contiguous() and mu.shape == (n, d) and mu.is_contiguous(),
+              "token_shift_mix: operands")
+        _need(prev.dtype == torch.float32 and prev.stride(1) == 1 and prev.shape[1] == d,
+              "token_shift_mix: bad previous rows")
+        _need(out.dtype == h.dtype and out.is_contiguous() and out.shape[1:] == (t, d)
+              and out.shape[0] >= (n - 1 if out_f32 is not None else n), "token_shift_mix: out")
+        _need(out_f32 is None or (out_f32.shape == (t, d) and out_f32.dtype == torch.float32
+                                  and out_f32.is_contiguous()), "token_shift_mix: float32 out")
+        self.launches += 1
+        _check(self._part_lib("shortconv")["shift_mix"](
+            _ptr(h), _code(h.dtype), _ptr(mu), _code(mu.dtype), n, _ptr(prev), prev.stride(0),
+            _ptr(step.state_slot), _ptr(step.cu_q), _ptr(step.req_of_token), _ptr(out),
+            _ptr(out_f32), t, d, self._stream()), "token_shift_mix")
+
+    def linear_scan(self, a, k, v, state, step, n_heads: int, e: int, f: int, out,
+                    decay_tok=None, decay_head=None, bonus=None, read_first: bool = False) -> None:
+        """Walk every request's tokens through the matrix state ``S [e, f]`` of every head.
+        ``a``, ``k``, ``v``: (tensor [T, *], first column) of the read vector, keys and
+        values.  ``decay_tok [T, H*e]`` float32 (a decay per token and key channel) or
+        ``decay_head [H]`` float32 (one a head).  ``read_first``: the token reads
+        ``S + diag(bonus) k v^T`` and the state moves on afterwards; else the state takes
+        the token in and is then read.  ``state [slots, >= H*e*f]`` float32, ``out [T, H*f]``
+        float32."""
+        t = step.n_tokens
+        for (src, off), width in ((a, e), (k, e), (v, f)):
+            _need(src.is_contiguous() and src.shape[0] >= t
+                  and src.shape[1] >= off + n_heads * width, "linear_scan: bad operand")
+        _need(state.dtype == torch.float32 and state.stride(1) == 1
+              and state.shape[1] >= n_heads * e * f, "linear_scan: bad state")
+        _need(out.shape == (t, n_heads * f) and out.dtype == torch.float32 and out.is_contiguous(),
+              "linear_scan: bad out")
+        _need((decay_tok is None) != (decay_head is None), "linear_scan: one kind of decay")
+        _need(decay_tok is None or (decay_tok.shape == (t, n_heads * e) and decay_tok.is_contiguous()
+                                    and decay_tok.dtype == torch.float32), "linear_scan: decay")
+        _need(decay_head is None or (decay_head.shape == (n_heads,)
+                                     and decay_head.dtype == torch.float32), "linear_scan: decay")
+        _need(bonus is None or (bonus.numel() == n_heads * e and bonus.is_contiguous()),
+              "linear_scan: bad bonus")
+        self.launches += 1
+        _check(self._part_lib("scan")["scan"](
+            _ptr(a[0]), _code(a[0].dtype), a[0].shape[1], a[1],
+            _ptr(k[0]), _code(k[0].dtype), k[0].shape[1], k[1],
+            _ptr(v[0]), _code(v[0].dtype), v[0].shape[1], v[1],
+            _ptr(decay_tok), n_heads * e, _ptr(decay_head), _ptr(bonus),
+            _code(bonus.dtype) if bonus is not None else 0, 1 if read_first else 0,
+            _ptr(step.cu_q), _ptr(step.state_slot), _ptr(state), state.stride(0),
+            step.n_requests, n_heads, e, f, _ptr(out), self._stream()), "linear_scan")
+
+    def scan_finish(self, o, gate, gate_off: int, weight, eps: float, out, n_heads: int,
+                    f: int) -> None:
+        """``out = o / rms_per_head(o) * weight * silu(gate)`` (``weight`` may be None)."""
+        t = o.shape[0]
+        _need(o.shape == (t, n_heads * f) and o.dtype == torch.float32 and o.is_contiguous()
+              and out.shape == (t, n_heads * f) and out.is_contiguous()
+              and out.dtype == gate.dtype and gate.is_contiguous()
+              and gate.shape[1] >= gate_off + n_heads * f, "scan_finish: operands")
+        _need(weight is None or weight.shape == (n_heads * f,), "scan_finish: bad weight")
+        self.launches += 1
+        _check(self._part_lib("scan")["finish"](
+            _ptr(o), _ptr(gate), _code(gate.dtype), gate.shape[1], gate_off, _ptr(weight),
+            _code(weight.dtype) if weight is not None else 0, float(eps), _ptr(out), t, n_heads,
+            f, self._stream()), "scan_finish")
+
+    def rotate_rows(self, src, q_off: int, k_off: int, positions, freq, dims: int,
+                    k_scale: float, out, n_heads: int, e: int) -> None:
+        """``out[t] = [rot(q) | rot(k) * k_scale]`` in float32: the first ``dims`` entries of
+        every head rotated by position * ``freq`` (float64), entry i paired with i + dims/2."""
+        t = out.shape[0]
+        _need(src.is_contiguous() and src.shape[0] >= t and out.shape == (t, 2 * n_heads * e)
+              and out.dtype == torch.float32 and out.is_contiguous(), "rotate_rows: operands")
+        _need(dims == 0 or (freq.dtype == torch.float64 and freq.numel() == dims // 2),
+              "rotate_rows: bad frequencies")
+        self.launches += 1
+        _check(self._part_lib("scan")["rotate"](
+            _ptr(src), _code(src.dtype), src.shape[1], q_off, k_off, _ptr(positions),
+            _ptr(freq) if dims else None, dims, float(k_scale), _ptr(out), t, n_heads, e,
+            self._stream()), "rotate_rows")
+
+    def decay_lowrank(self, lo, w2, w0, out) -> None:
+        """``out = exp(-exp(tanh(lo) @ w2^T + w0))``, all float32."""
+        t, rank = lo.shape
+        c = w2.shape[0]
+        _need(lo.dtype == torch.float32 and lo.is_contiguous() and w2.shape == (c, rank)
+              and w2.dtype == torch.float32 and w2.is_contiguous() and w0.shape == (c,)
+              and out.shape == (t, c) and out.dtype == torch.float32 and out.is_contiguous(),
+              "decay_lowrank: operands")
+        self.launches += 1
+        _check(self._part_lib("scan")["decay"](
+            _ptr(lo), rank, _ptr(w2), _ptr(w0), _code(w0.dtype), _ptr(out), t, c, self._stream()),
+            "decay_lowrank")
 
     def sample(self, logits, temperature, uniform, out) -> None:
         """Tokens for float32 ``logits [n, V]``; rows with temperature <= 0 (or

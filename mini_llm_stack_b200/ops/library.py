@@ -46,6 +46,8 @@ MODULES = {
     "latent": ["latent.cu"],
     "mlstm": ["mlstm.cu"],
     "experts": ["experts.cu"],
+    "shortconv": ["short_conv.cu"],
+    "scan": ["linear_scan.cu"],
 }
 
 
@@ -57,7 +59,8 @@ def all_modules(head_sizes=()) -> list:
     if (CSRC / "gemm_tcgen05.cu").is_file():
         out.append(("gemm", {}))
     out.append(("argmax_static", {}))
-    out += [(name, {}) for name in ("layernorm", "latent", "mlstm", "experts")]
+    out += [(name, {}) for name in ("layernorm", "latent", "mlstm", "experts", "shortconv",
+                                    "scan")]
     return out
 
 

@@ -14,7 +14,7 @@ Every part:
 Norm:
     forward(stream, rows=None) -> h               stream.settle + normalise
 Mixer:
-    cache_spec() -> PagedKV | FixedState | None   what it keeps per request
+    cache_spec() -> PagedKV | FixedState | PagedWithState | None   what it keeps per request
     forward(h, step, cache) -> delta [T, d_model]
 FeedForward:
     forward(h, step) -> delta [T, d_model]
@@ -69,6 +69,15 @@ class FixedState:
     """Per-request state whose size does not grow with the sequence."""
     shape: tuple
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class PagedWithState:
+    """Pages and, beside them, a state of fixed size (a mixer whose keys pass through a
+    short convolution keeps the convolution's last inputs of every request).  The
+    handle of such a slot is a paged one that also carries ``state``."""
+    paged: PagedKV
+    state: FixedState
 
 
 # ----------------------------------------------------------------------------

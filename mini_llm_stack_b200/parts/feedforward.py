@@ -1,4 +1,5 @@
-"""Feed-forwards: dense SwiGLU, a clamped gated unit, and routed experts.
+"""Feed-forwards: dense SwiGLU, a clamped gated unit, an ungated unit with the square of
+relu, and routed experts.
 
 Reference (train/model.py:127-135): ``w_down(silu(w_gate x) * (w_up x))`` with
 ``silu(z) = z * sigmoid(z)``, no biases.  Gate and up share one projection
@@ -101,6 +102,35 @@ class ClampedGLUFeedForward(FeedForward):
             gu = rt.buffer("gate_up", (t, 2 * i), rt.act_dtype)
             rt.ops.linear(h, self.w_gate_up, gu)
             rt.ops.clamped_glu(gu, act, self.alpha, self.limit)
+        delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)
+        return rt.ops.linear_parts(act, self.w_down, delta)
+
+
+class SquaredReluFeedForward(FeedForward):
+    """``W_down relu(W_up h)^2``: no gate, no biases.  The activation runs in float32 on
+    the projection's output."""
+
+    decode_capturable = prompt_capturable = True
+
+    def __init__(self, d_model: int, intermediate_size: int, names=("up", "down")):
+        self.d_model, self.intermediate_size = int(d_model), int(intermediate_size)
+        self.names = tuple(names)
+
+    def tensor_specs(self) -> dict:
+        d, i = self.d_model, self.intermediate_size
+        return {self.names[0]: TensorSpec((i, d)), self.names[1]: TensorSpec((d, i))}
+
+    def bind(self, tensors: dict, runtime) -> None:
+        self.runtime = runtime
+        self.w_up = runtime.ops.prepare_weight(tensors[self.names[0]])
+        self.w_down = runtime.ops.prepare_weight(tensors[self.names[1]])
+
+    def forward(self, h, step: StepContext):
+        rt = self.runtime
+        t = h.shape[0]
+        act = rt.buffer("ffn_act", (t, self.intermediate_size), rt.act_dtype)
+        rt.ops.linear(h, self.w_up, act)
+        rt.ops.relu_squared(act, act)
         delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)
         return rt.ops.linear_parts(act, self.w_down, delta)
 

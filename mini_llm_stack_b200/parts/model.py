@@ -47,19 +47,58 @@ class PassEntry(Part):
         self.runtime = runtime
         self.table = tensors[self.tensor_name].contiguous()
 
+    def needs_embedding(self, number: int) -> bool:
+        return self.add_embedding and number > 0
+
     def forward(self, stream: ResidualStream, number: int, embedded) -> None:
         stream.push_more(rows=embedded if (self.add_embedding and number > 0) else None,
                          vec=self.table[number])
 
 
-class TokenEmbedding(Part):
-    """``x[t] = E[token[t]]``; no scaling, no position term (train/model.py:239)."""
+class PassProjection(Part):
+    """What happens to the residual stream at the start of every pass over a run of layers
+    that is repeated (the first pass too): ``x <- W [x; x0]`` with x0 the embedding's
+    output and ``W [d_model, 2 d_model]`` (x's columns first).  The stream's waiting
+    addends are settled first; the product is written over the stream in float32."""
 
     decode_capturable = prompt_capturable = True
 
-    def __init__(self, vocab_size: int, d_model: int, tensor_name: str = "weight"):
+    def __init__(self, d_model: int, tensor_name: str = "in"):
+        self.d_model, self.tensor_name = int(d_model), tensor_name
+        self.weight = None
+
+    def tensor_specs(self) -> dict:
+        return {self.tensor_name: TensorSpec((self.d_model, 2 * self.d_model))}
+
+    def bind(self, tensors: dict, runtime) -> None:
+        self.runtime = runtime
+        self.weight = runtime.ops.prepare_weight(tensors[self.tensor_name])
+        runtime.ops.require_part("layernorm")        # the stream's helpers live there
+
+    def needs_embedding(self, number: int) -> bool:
+        return True
+
+    def forward(self, stream: ResidualStream, number: int, embedded) -> None:
+        rt = self.runtime
+        more_rows, more_vec = stream.take_more()
+        if more_rows is not None or more_vec is not None:
+            rt.ops.residual_add(stream.x, more_rows, more_vec)
+        t = stream.x.shape[0]
+        both = rt.buffer("pass_in", (t, 2 * self.d_model), rt.act_dtype)
+        rt.ops.settle_concat(stream.x, stream.take_pending(), embedded, both)
+        rt.ops.linear(both, self.weight, stream.x)
+
+
+class TokenEmbedding(Part):
+    """``x[t] = E[token[t]] * scale``; no position term.  (The reference has no scaling
+    either: ``scale`` 1, train/model.py:239.)"""
+
+    decode_capturable = prompt_capturable = True
+
+    def __init__(self, vocab_size: int, d_model: int, tensor_name: str = "weight",
+                 scale: float = 1.0):
         self.vocab_size, self.d_model = int(vocab_size), int(d_model)
-        self.tensor_name = tensor_name
+        self.tensor_name, self.scale = tensor_name, float(scale)
         self.weight = None
 
     def tensor_specs(self) -> dict:
@@ -72,34 +111,38 @@ class TokenEmbedding(Part):
     def forward(self, step: StepContext, buffer: str = "residual"):
         rt = self.runtime
         x = rt.buffer(buffer, (step.n_tokens, self.d_model), rt.residual_dtype)
-        rt.ops.embed(step.token_ids, self.weight, x, self.vocab_size)
+        rt.ops.embed(step.token_ids, self.weight, x, self.vocab_size, self.scale)
         return x
 
 
 class OutputHead(Part):
-    """``logits = h @ W^T`` in float32; W is the embedding table when tied."""
+    """``logits = (h @ W^T) * scale`` in float32; W is the embedding table when tied."""
 
     decode_capturable = prompt_capturable = True
 
-    def __init__(self, vocab_size: int, d_model: int, tied_to: Optional[TokenEmbedding]):
+    def __init__(self, vocab_size: int, d_model: int, tied_to: Optional[TokenEmbedding],
+                 tensor_name: str = "weight", scale: float = 1.0):
         self.vocab_size, self.d_model = int(vocab_size), int(d_model)
         self.tied_to = tied_to
+        self.tensor_name, self.scale = tensor_name, float(scale)
         self.weight = None
 
     def tensor_specs(self) -> dict:
         if self.tied_to is not None:
             return {}
-        return {"weight": TensorSpec((self.vocab_size, self.d_model))}
+        return {self.tensor_name: TensorSpec((self.vocab_size, self.d_model))}
 
     def bind(self, tensors: dict, runtime) -> None:
         self.runtime = runtime
-        w = self.tied_to.weight if self.tied_to is not None else tensors["weight"]
+        w = self.tied_to.weight if self.tied_to is not None else tensors[self.tensor_name]
         self.weight = runtime.ops.prepare_weight(w)
 
     def forward(self, h, n_rows: int):
         rt = self.runtime
         logits = rt.buffer("logits", (n_rows, self.vocab_size), rt.logits_dtype)
         rt.ops.linear(h, self.weight, logits)
+        if self.scale != 1.0:
+            rt.ops.scale_(logits, self.scale)
         return logits
 
 
@@ -211,7 +254,8 @@ class ComposedModel:
         self.runtime.ops.begin_step(step.n_tokens)
         stream = ResidualStream(self.embedding.forward(step))
         embedded = None
-        if any(c.entry is not None and c.entry[1] > 0 for c in self.calls):
+        if any(c.entry is not None and self.entries[c.entry[0]][1].needs_embedding(c.entry[1])
+               for c in self.calls):
             # the stream moves on in place: a pass that starts over from the embedding's
             # output reads a second copy of it
             embedded = self.embedding.forward(step, buffer="embedded")

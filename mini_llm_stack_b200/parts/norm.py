@@ -15,17 +15,19 @@ from .base import Norm, ResidualStream, TensorSpec
 class RMSNorm(Norm):
     decode_capturable = prompt_capturable = True   # forward only launches kernels on the current stream
 
-    def __init__(self, dim: int, eps: float):
+    def __init__(self, dim: int, eps: float, tensor_name: str = "weight"):
+        """``tensor_name``: the local name of the weight ("" = the part's own prefix)."""
         self.dim = int(dim)
         self.eps = float(eps)
+        self.tensor_name = tensor_name
         self.weight = None
 
     def tensor_specs(self) -> dict:
-        return {"weight": TensorSpec((self.dim,), kind="vector", init="ones")}
+        return {self.tensor_name: TensorSpec((self.dim,), kind="vector", init="ones")}
 
     def bind(self, tensors: dict, runtime) -> None:
         self.runtime = runtime
-        self.weight = tensors["weight"].contiguous()
+        self.weight = tensors[self.tensor_name].contiguous()
 
     def forward(self, stream: ResidualStream, rows=None, n_rows: int = 0):
         """Add the pending delta into the stream, return the normalised rows.
@@ -37,8 +39,7 @@ class RMSNorm(Norm):
         rt = self.runtime
         more_rows, more_vec = stream.take_more()
         if more_rows is not None or more_vec is not None:
-            if rows is not None:
-                raise RuntimeError("addends beside the delta cannot be settled for picked rows")
+            # (also before picked rows: the addends go into every row of the stream)
             rt.ops.residual_add(stream.x, more_rows, more_vec)
         delta = stream.take_pending()
         if rows is None:

@@ -1,4 +1,6 @@
-"""Rotary position encoding, rotate-half pairing.
+"""Rotary position encoding: rotate-half pairing over the whole head by table
+(``RotaryPosition``), and a rotation of a head's first entries with either pairing and
+scaled frequencies (``PartialRotary``).
 
 Reference (train/model.py:36-52): ``inv_freq[i] = theta ** -(2i / head_dim)``
 for i in [0, head_dim/2); ``angle[p, i] = p * inv_freq[i]``; cos and sin tables
@@ -67,3 +69,36 @@ class RotaryPosition(PositionEncoding):
             qkv, step.positions, self.cos, self.sin, g.slot_map,
             cache.k_pool, cache.v_pool, step.n_tokens, n_heads, n_kv_heads,
             self.head_dim, self.max_positions, cache.writes, parts=parts)
+
+
+class PartialRotary(PositionEncoding):
+    """Rotation of the first ``dims`` entries of every head; the rest pass unchanged.
+
+    The pair number i (0 <= i < dims/2) at position p turns by the angle
+    ``p * base^(-2i/dims) / factor`` (``factor``: linear scaling of the frequencies):
+    ``(u, v) -> (u cos - v sin, v cos + u sin)``.  ``pairing`` says which entries form
+    pair i: "interleaved" (2i, 2i + 1) or "half" (i, i + dims/2).  There is no table
+    and so no bound on the positions: the kernels that rotate form the angle in float64
+    from the position and this part's float64 frequencies, and round its cosine and
+    sine once to float32."""
+
+    decode_capturable = prompt_capturable = True
+
+    def __init__(self, dims: int, base: float, factor: float = 1.0, pairing: str = "half"):
+        if pairing not in ("interleaved", "half"):
+            raise ValueError(f"pairing must be 'interleaved' or 'half', not {pairing!r}")
+        if dims < 0 or dims % 2:
+            raise ValueError("the rotated entries of a head come in pairs")
+        self.dims, self.base, self.factor = int(dims), float(base), float(factor)
+        self.pairing = pairing
+        self.freq = None
+
+    def frequencies(self):
+        """``base^(-2i/dims) / factor`` for i < dims/2, float64 on the host."""
+        i = torch.arange(self.dims // 2, dtype=torch.float64)
+        return torch.pow(torch.tensor(self.base, dtype=torch.float64),
+                         -2.0 * i / max(self.dims, 1)) / self.factor
+
+    def bind(self, tensors: dict, runtime) -> None:
+        self.runtime = runtime
+        self.freq = self.frequencies().to(runtime.device).contiguous()
