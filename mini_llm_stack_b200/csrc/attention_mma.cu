@@ -53,9 +53,22 @@ struct Params {
     int cluster_merge;                   // split TMA kernel: the splits of a request and kv head are
                                          // one cluster and merge through shared memory
     float scale_log2;                    // scale * log2(e)
+    float cap_log2, tanh_arg;            // a cap c on the scores: c * log2(e) and 2 log2(e) scale / c
+                                         // (cap_log2 = 0: none)
     int* status;                         // device status word (a bounded wait that ran out)
     long long n_pages;                   // pages of the pool: [Hkv, pages, block, HD]
 };
+
+// A raw score q . k in the log2 domain of the softmax: times scale * log2(e), or, with a cap
+// c on the scores, c * tanh(raw * scale / c) * log2(e) with tanh(x) = 1 - 2 / (1 + e^(2x)).
+__device__ __forceinline__ float score_log2(float raw, const Params& P) {
+    if (P.cap_log2 > 0.f) {
+        float e;
+        asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(fminf(raw * P.tanh_arg, 80.f)));
+        return P.cap_log2 * (1.0f - __fdividef(2.0f, 1.0f + e));
+    }
+    return raw * P.scale_log2;
+}
 
 // What the split kernel needs to take the rotation and the cache write upon itself in a
 // step of single decoded tokens (parts == nullptr: it does not).  The q/k/v projection is
@@ -267,8 +280,8 @@ __global__ void __launch_bounds__(NT) attention_tile_kernel(const Params P) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int jj = j + e;
-                const float a = (jj <= pA && jj >= loA) ? s[n][e] * P.scale_log2 : -INFINITY;
-                const float b = (jj <= pB && jj >= loB) ? s[n][2 + e] * P.scale_log2 : -INFINITY;
+                const float a = (jj <= pA && jj >= loA) ? score_log2(s[n][e], P) : -INFINITY;
+                const float b = (jj <= pB && jj >= loB) ? score_log2(s[n][2 + e], P) : -INFINITY;
                 s[n][e] = a;
                 s[n][2 + e] = b;
                 tmA = fmaxf(tmA, a);
@@ -429,8 +442,8 @@ __global__ void __launch_bounds__(NT) attention_split_kernel(const Params P) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int jj = j + e;
-                const float a = (jj <= pA && jj >= loA) ? s[n][e] * P.scale_log2 : -INFINITY;
-                const float b = (jj <= pB && jj >= loB) ? s[n][2 + e] * P.scale_log2 : -INFINITY;
+                const float a = (jj <= pA && jj >= loA) ? score_log2(s[n][e], P) : -INFINITY;
+                const float b = (jj <= pB && jj >= loB) ? score_log2(s[n][2 + e], P) : -INFINITY;
                 s[n][e] = a;
                 s[n][2 + e] = b;
                 tmA = fmaxf(tmA, a);
@@ -958,8 +971,8 @@ attention_split_tma_kernel(const Params P, const Fused F,
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int jj = j + e;
-                const float a = (jj <= pA && jj >= loA) ? s[n][e] * P.scale_log2 : -INFINITY;
-                const float b = (jj <= pB && jj >= loB) ? s[n][2 + e] * P.scale_log2 : -INFINITY;
+                const float a = (jj <= pA && jj >= loA) ? score_log2(s[n][e], P) : -INFINITY;
+                const float b = (jj <= pB && jj >= loB) ? score_log2(s[n][2 + e], P) : -INFINITY;
                 s[n][e] = a;
                 s[n][2 + e] = b;
                 tmA = fmaxf(tmA, a);
@@ -1244,8 +1257,8 @@ attention_tile_tma_kernel(const Params P, const __grid_constant__ CUtensorMap km
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int jj = j + e;
-                    const float a = (jj <= pA && jj >= loA) ? s[n][e] * P.scale_log2 : -INFINITY;
-                    const float b = (jj <= pB && jj >= loB) ? s[n][2 + e] * P.scale_log2 : -INFINITY;
+                    const float a = (jj <= pA && jj >= loA) ? score_log2(s[n][e], P) : -INFINITY;
+                    const float b = (jj <= pB && jj >= loB) ? score_log2(s[n][2 + e], P) : -INFINITY;
                     s[n][e] = a;
                     s[n][2 + e] = b;
                     tmA = fmaxf(tmA, a);
@@ -1257,8 +1270,8 @@ attention_tile_tma_kernel(const Params P, const __grid_constant__ CUtensorMap km
             for (int n = 0; n < BN / 8; ++n) {
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
-                    s[n][e] *= P.scale_log2;
-                    s[n][2 + e] *= P.scale_log2;
+                    s[n][e] = score_log2(s[n][e], P);
+                    s[n][2 + e] = score_log2(s[n][2 + e], P);
                     tmA = fmaxf(tmA, s[n][e]);
                     tmB = fmaxf(tmB, s[n][2 + e]);
                 }
@@ -1399,15 +1412,17 @@ constexpr int SPLIT_SMEM_MERGE = (128 + 4 * 16 * HD) * 4;
 constexpr int SPLIT_SMEM = SPLIT_SMEM_PIPE > SPLIT_SMEM_MERGE ? SPLIT_SMEM_PIPE : SPLIT_SMEM_MERGE;
 }  // namespace
 
+// softcap c > 0: scores become c * tanh(score / c) before the softmax.
 // n_tiles: 64-row tiles the tile kernel has to run (0: none); n_small: 1 if any
 // request goes to the split kernel.  part_o / part_lse are scratch memory of
 // n_split * T * H * (HD + 1) floats, needed when n_split > 1.
 MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, const void* v_pool,
                               const int* block_table, int max_blocks, const int* cu_q,
                               const int* ctx_len, int n_req, int n_tokens, int n_heads, int n_kv,
-                              int block_size, float scale, int window, int n_tiles, int n_small,
-                              int n_split, float* part_o, float* part_lse, long long pool_pages,
-                              int* status, int use_tma, cudaStream_t stream) {
+                              int block_size, float scale, int window, float softcap, int n_tiles,
+                              int n_small, int n_split, float* part_o, float* part_lse,
+                              long long pool_pages, int* status, int use_tma,
+                              cudaStream_t stream) {
     if (n_tokens <= 0 || n_req <= 0) return 0;
     if (n_heads % n_kv || n_split < 1 || n_split > MAX_SPLITS ||
         (n_split > 1 && (!part_o || !part_lse)))
@@ -1444,6 +1459,8 @@ MLS_API int mls_attention_mma(const void* qkv, void* out, const void* k_pool, co
     P.small_only = n_small ? 1 : 0;
     P.cluster_merge = 0;
     P.scale_log2 = scale * LOG2E;
+    P.cap_log2 = softcap > 0.f ? softcap * LOG2E : 0.f;
+    P.tanh_arg = softcap > 0.f ? 2.0f * LOG2E * scale / softcap : 0.f;
     P.status = status;
     P.n_pages = pool_pages;
     const bool tma_ok = use_tma && (block_size == 8 || block_size == 16 || block_size == 32 ||
@@ -1520,6 +1537,7 @@ MLS_API int mls_attention_decode_fused(const float* parts, int n_parts, long lon
                                        int* status, cudaStream_t stream) {
 #if MLS_HEAD_DIM % 64 == 0
     if (n_req <= 0) return 0;
+    const float softcap = 0.f;           // the fused step has no cap on its scores
     if (n_heads % n_kv || n_heads / n_kv > 16 || n_split < 1 || n_split > MAX_SPLITS ||
         (n_split > 1 && (!part_o || !part_lse)) || !parts || n_parts < 1 || part_stride % 4 != 0)
         return MLS_ERR_UNSUPPORTED;
@@ -1559,6 +1577,8 @@ MLS_API int mls_attention_decode_fused(const float* parts, int n_parts, long lon
     P.small_only = 1;
     P.cluster_merge = 0;
     P.scale_log2 = scale * LOG2E;
+    P.cap_log2 = softcap > 0.f ? softcap * LOG2E : 0.f;
+    P.tanh_arg = softcap > 0.f ? 2.0f * LOG2E * scale / softcap : 0.f;
     P.status = status;
     P.n_pages = pool_pages;
     Fused F;

@@ -73,6 +73,8 @@ struct Params {
     int max_blocks, n_req, n_heads, n_kv, group, block_size, window, small_only;
     int two_tiles;                       // 1: a CTA owns two row tiles; 0: one, its keys in halves
     float scale_log2;
+    float cap_over_scale, tanh_arg;      // a cap c on the scores: c / scale and 2 log2(e) scale / c
+                                         // (cap_over_scale = 0: none)
     int* status;
     long long n_pages;                   // pages of the pool: [Hkv, pages, block, HD]
 };
@@ -366,6 +368,15 @@ attention_tc_kernel(const Params P, const __grid_constant__ CUtensorMap kmap,
                 for (int e = 0; e < 16; ++e) sc[c0 + e] = __uint_as_float(a[e]);
             }
             tmem_ld_wait();
+            if (P.cap_over_scale > 0.f) {
+                // capped scores, c * tanh(raw * scale / c), left in raw units (divided by the
+                // scale again) so that what follows is the same; tanh(x) = 1 - 2 / (1 + e^(2x))
+#pragma unroll
+                for (int e = 0; e < BN; ++e) {
+                    const float ex = fast_exp2(fminf(sc[e] * P.tanh_arg, 80.f));
+                    sc[e] = P.cap_over_scale * (1.0f - __fdividef(2.0f, 1.0f + ex));
+                }
+            }
             const bool masked = kbase + BN - 1 > pos || kbase < lo_row;
             if (__any_sync(0xffffffffu, masked)) {
 #pragma unroll
@@ -571,7 +582,7 @@ MLS_API int mls_attention_tc_rows() {
 MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, const void* v_pool,
                              const int* block_table, int max_blocks, const int* cu_q,
                              const int* ctx_len, int n_req, int n_heads, int n_kv, int block_size,
-                             float scale, int window, int n_tiles, int n_tiles_wide,
+                             float scale, int window, float softcap, int n_tiles, int n_tiles_wide,
                              int skip_small, long long pool_pages, int* status,
                              cudaStream_t stream) {
 #if MLS_HEAD_DIM == 64 || MLS_HEAD_DIM == 128
@@ -609,6 +620,8 @@ MLS_API int mls_attention_tc(const void* qkv, void* out, const void* k_pool, con
     if (g_forced_rows == CHAIN_ROWS) P.two_tiles = 0;
     if (g_forced_rows == 2 * CHAIN_ROWS && n_tiles_wide > 0) P.two_tiles = 1;
     P.scale_log2 = scale * LOG2E;
+    P.cap_over_scale = softcap > 0.f ? softcap / scale : 0.f;
+    P.tanh_arg = softcap > 0.f ? 2.0f * LOG2E * scale / softcap : 0.f;
     P.status = status;
     P.n_pages = pool_pages;
     MLS_LAUNCH((attention_tc_kernel), dim3(n_kv, P.two_tiles ? n_tiles_wide : n_tiles),

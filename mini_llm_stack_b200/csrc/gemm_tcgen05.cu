@@ -42,7 +42,8 @@ struct GemmParams {
     int out_f32;                         // 1: out is float32
     int transposed;                      // 1: store D^T (out[n][m])
     int splits;                          // parts along K
-    int epilogue;                        // 0: store D; 1: gated unit over interleaved gate / up blocks of 16
+    int epilogue;                        // 0: store D; 1: gated unit over interleaved gate / up blocks of 16;
+                                         // 2: the square of relu on every output
     // the gated unit: g' = min(g, limit), u' = clamp(u, -limit, limit) (limit <= 0: as they
     // are), out = g' * sigmoid(alpha * g') * (u' + shift); SwiGLU is (1, 0, 0)
     float glu_alpha = 1.f, glu_limit = 0.f, glu_shift = 0.f;
@@ -85,6 +86,14 @@ __device__ __forceinline__ float gated(float g, float u, float alpha, float limi
     return (g / (1.0f + expf(-alpha * g))) * (u + shift);
 }
 #define GATED(p, g, u) gated(g, u, (p).glu_alpha, (p).glu_limit, (p).glu_shift)
+// An activation without a gate on a finished output (epilogue 2: relu(x)^2; else x).
+__device__ __forceinline__ float ungated(int epilogue, float x) {
+    if (epilogue == 2) {
+        x = fmaxf(x, 0.f);
+        return x * x;
+    }
+    return x;
+}
 
 // Store 16 consecutive columns (col0 ..) of D's row `row`.  With the SwiGLU
 // epilogue `v` holds 16 gate columns and `u` the 16 matching up columns.
@@ -100,7 +109,7 @@ __device__ __forceinline__ void store_normal(const GemmParams& p, int row, int c
         width = p.nn >> 1;
     } else {
 #pragma unroll
-        for (int e = 0; e < 16; ++e) r[e] = v[e];
+        for (int e = 0; e < 16; ++e) r[e] = ungated(p.epilogue, v[e]);
     }
     const size_t at = (size_t)row * p.ld_out + col;
     const bool whole = col + 16 <= width && (p.ld_out % 8) == 0;
@@ -147,6 +156,8 @@ __device__ __forceinline__ void store_transposed(const GemmParams& p, int row, i
             feature = ((row - lane) >> 1) + lane;
             width = p.mm >> 1;
             mine = lane < 16;
+        } else {
+            val = ungated(p.epilogue, val);
         }
         if (col < p.nn && mine && feature < width && row < p.mm) {
             const size_t at = (size_t)col * p.ld_out + feature;
@@ -588,8 +599,8 @@ gemm_tcgen05_pair_kernel(const GemmParams p, const __grid_constant__ CUtensorMap
                             tmem_ld_wait();
 #pragma unroll
                             for (int e = 0; e < 16; ++e) {
-                                r[e] = __uint_as_float(a[e]);
-                                r[16 + e] = __uint_as_float(b[e]);
+                                r[e] = ungated(p.epilogue, __uint_as_float(a[e]));
+                                r[16 + e] = ungated(p.epilogue, __uint_as_float(b[e]));
                             }
                         }
 #pragma unroll
@@ -688,6 +699,7 @@ __global__ void splitk_sum_kernel(const float* __restrict__ partial, void* __res
         } else {
             r = 0.f;
             for (int k = 0; k < splits; ++k) r += partial[(size_t)k * n + i];
+            r = ungated(epilogue, r);
         }
         if (out_f32) ((float*)out)[i] = r;
         else ((__nv_bfloat16*)out)[i] = __float2bfloat16_rn(r);
@@ -726,6 +738,7 @@ __global__ void pair_tail_sum_kernel(const GemmParams p, int m_pairs, int tail_t
             v = 0.f;
 #pragma unroll 8
             for (int k = 0; k < p.tail_parts; ++k) v += src[k * part_stride + o];
+            v = ungated(p.epilogue, v);
         }
         const size_t at = (size_t)row * p.ld_out + col;
         if (p.out_f32) ((float*)p.out)[at] = v;
@@ -922,7 +935,8 @@ MLS_API long long mls_gemm_prompt_scratch_floats(int m, int n, int k) {
 // splits * M * N, which a second kernel adds up (with out == nullptr the parts are left
 // to the caller, [part][M][N]).  With swap = 0 `partial` is optional scratch of
 // mls_gemm_prompt_scratch_floats(m, n, k) floats.  epilogue 1: the weight rows alternate
-// between 16 gate rows and the 16 matching up rows, and out[M, N / 2] = silu(gate) * up.
+// between 16 gate rows and the 16 matching up rows, and out[M, N / 2] = silu(gate) * up;
+// epilogue 2: out = relu(act . w^T)^2.
 static int gemm_bf16(const void* act, const void* w, void* out, int out_f32, int m, int n, int k,
                      int swap, int splits, int epilogue, float* partial, int* status,
                      cudaStream_t stream, float alpha, float limit, float shift) {

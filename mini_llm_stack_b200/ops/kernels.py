@@ -442,6 +442,22 @@ class Ops:
             return
         self._gemm_bf16(a, w_interleaved, out, m, n, k, epilogue=1, gate=(alpha, limit, 1.0))
 
+    def can_fuse_activation(self, k: int) -> bool:
+        """Whether a product and an ungated activation of its outputs can run as one kernel."""
+        return (self.act_dtype == torch.bfloat16 and self.gemm_impl != "cublas" and k % 8 == 0)
+
+    def linear_relu_squared(self, a, w, out) -> None:
+        """``out[M, N] = relu(a @ w^T)^2`` in one kernel (the tcgen05 product's epilogue)."""
+        m, k = a.shape
+        n = w.shape[0]
+        _need(w.shape == (n, k) and out.shape == (m, n) and a.dtype == torch.bfloat16
+              and w.dtype == torch.bfloat16, "linear_relu_squared: shapes or types do not fit")
+        _need(a.is_contiguous() and w.is_contiguous() and out.is_contiguous(),
+              "linear_relu_squared: operands must be contiguous")
+        if m == 0:
+            return
+        self._gemm_bf16(a, w, out, m, n, k, epilogue=2)
+
     def rope_takes_parts(self, hd: int) -> bool:
         """Whether ``rope_store`` can read its rows from a product's K-parts."""
         return self.act_dtype == torch.bfloat16 and (hd // 2) % 8 == 0
@@ -486,10 +502,11 @@ class Ops:
         if self.act_dtype == torch.bfloat16 and hd not in self._attention_libs:
             lib = self._load("attention", {"MLS_HEAD_DIM": int(hd)})
             fn = _decl(lib, "mls_attention_mma",
-                       [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _I, _I, _I,
+                       [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _I, _F, _I, _I, _I,
                         _P, _P, _LL, _P, _I, _P])
             tc = _decl(lib, "mls_attention_tc",
-                       [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _I, _I, _I, _LL, _P, _P])
+                       [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _F, _I, _F, _I, _I, _I, _LL,
+                        _P, _P])
             fused = _decl(lib, "mls_attention_decode_fused",
                           [_P, _I, _LL, _P, _P, _P, _I, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I,
                            _I, _I, _F, _I, _I, _P, _P, _LL, _P, _P])
@@ -512,13 +529,13 @@ class Ops:
         fn = _decl(lib, "mls_attention_tc_set_rows", [_I], restype=None)
         fn(rows)
 
-    def attention_tensor_cores(self, hd: int, softcap: float = 0.0) -> bool:
+    def attention_tensor_cores(self, hd: int) -> bool:
         """Whether the tensor-core attention kernels take this step's attention (else
-        the one-warp-per-row kernel does, which takes every size and option)."""
+        the one-warp-per-row kernel does, which takes every head size up to 512)."""
         return (self.act_dtype == torch.bfloat16 and self.attention_impl != "simt"
-                and hd <= 256 and not softcap)
+                and hd <= 256 and hd % 16 == 0)
 
-    def attention_facts(self, hd: int, softcap: float = 0.0) -> dict:
+    def attention_facts(self, hd: int) -> dict:
         """What a mixer needs to know of the attention kernels to plan a step's
         launches: ``small_rows`` (requests whose (token, head) rows of one kv head are
         at most this many go to the context-split kernel), ``tile_rows`` and
@@ -537,7 +554,7 @@ class Ops:
                 # takes over beyond that)
                 "cluster_splits": 8 if tma and os.environ.get(
                     "MLS_B200_CLUSTER_MERGE", "1") != "0" else 0,
-                "tensor_cores": self.attention_tensor_cores(hd, softcap)}
+                "tensor_cores": self.attention_tensor_cores(hd)}
 
     def paged_attention(self, qkv, out, cache, step, n_heads: int, n_kv: int, hd: int,
                         scale: float, window: int, plan=None, softcap: float = 0.0) -> None:
@@ -549,7 +566,7 @@ class Ops:
         t = step.n_tokens
         _need(out.shape == (t, n_heads * hd) and out.is_contiguous(), "attention: bad out")
         _need(cache.k_pool.dtype == qkv.dtype, "attention: cache and activations differ")
-        if self.attention_tensor_cores(hd, softcap) and qkv.dtype == torch.bfloat16:
+        if self.attention_tensor_cores(hd) and qkv.dtype == torch.bfloat16:
             fns = self._attention_libs.get(hd)
             _need(fns is not None, f"attention kernels for head size {hd} were not required")
             fn, tc = fns
@@ -564,7 +581,7 @@ class Ops:
                 _check(tc(_ptr(qkv), _ptr(out), _ptr(cache.k_pool), _ptr(cache.v_pool),
                           _ptr(g.block_table), g.max_blocks, _ptr(step.cu_q), _ptr(step.ctx_len),
                           step.n_requests, n_heads, n_kv, g.block_size, float(scale), int(window),
-                          n_tiles_tc, plan.n_tiles_tc_wide, n_small, cache.k_pool.shape[1],
+                          float(softcap), n_tiles_tc, plan.n_tiles_tc_wide, n_small, cache.k_pool.shape[1],
                           _ptr(self.status), self._stream()), "attention_tc")
                 n_tiles = 0
                 if not n_small:
@@ -582,7 +599,7 @@ class Ops:
             _check(fn(_ptr(qkv), _ptr(out), _ptr(cache.k_pool), _ptr(cache.v_pool),
                       _ptr(g.block_table), g.max_blocks, _ptr(step.cu_q), _ptr(step.ctx_len),
                       step.n_requests, t, n_heads, n_kv, g.block_size, float(scale), int(window),
-                      n_tiles, n_small, n_split, _ptr(part_o), _ptr(part_lse),
+                      float(softcap), n_tiles, n_small, n_split, _ptr(part_o), _ptr(part_lse),
                       cache.k_pool.shape[1], _ptr(self.status),
                       0 if self.attention_impl == "no_tma" else 1, self._stream()),
                    "attention_mma")

@@ -77,9 +77,9 @@ class ConvKeyAttention(Mixer):
             self.position.bind({}, runtime)
         ops.require_part("shortconv")
         ops.require_part("layernorm")
-        if ops.attention_tensor_cores(self.head_dim, self.softcap):
+        if ops.attention_tensor_cores(self.head_dim):
             ops.require_attention(self.head_dim, self.n_heads, self.n_kv_heads)
-        self._facts = ops.attention_facts(self.head_dim, self.softcap)
+        self._facts = ops.attention_facts(self.head_dim)
 
     def plan(self, step: StepContext):
         return plan_paged_attention(step, self._facts, self.n_heads, self.n_kv_heads,

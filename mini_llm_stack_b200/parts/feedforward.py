@@ -107,8 +107,9 @@ class ClampedGLUFeedForward(FeedForward):
 
 
 class SquaredReluFeedForward(FeedForward):
-    """``W_down relu(W_up h)^2``: no gate, no biases.  The activation runs in float32 on
-    the projection's output."""
+    """``W_down relu(W_up h)^2``: no gate, no biases.  The activation runs in float32, in
+    the projection's own epilogue where the tcgen05 kernel takes the sizes (as
+    ``SwiGLUFeedForward`` does), else on the projection's output."""
 
     decode_capturable = prompt_capturable = True
 
@@ -124,13 +125,18 @@ class SquaredReluFeedForward(FeedForward):
         self.runtime = runtime
         self.w_up = runtime.ops.prepare_weight(tensors[self.names[0]])
         self.w_down = runtime.ops.prepare_weight(tensors[self.names[1]])
+        self.fused = (self.w_up.dtype == torch.bfloat16
+                      and runtime.ops.can_fuse_activation(self.d_model))
 
     def forward(self, h, step: StepContext):
         rt = self.runtime
         t = h.shape[0]
         act = rt.buffer("ffn_act", (t, self.intermediate_size), rt.act_dtype)
-        rt.ops.linear(h, self.w_up, act)
-        rt.ops.relu_squared(act, act)
+        if self.fused:
+            rt.ops.linear_relu_squared(h, self.w_up, act)
+        else:
+            rt.ops.linear(h, self.w_up, act)
+            rt.ops.relu_squared(act, act)
         delta = rt.buffer("delta", (t, self.d_model), rt.act_dtype)
         return rt.ops.linear_parts(act, self.w_down, delta)
 
