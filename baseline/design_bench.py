@@ -1,5 +1,6 @@
-"""``bench.py --design zededra``: prefill and decode throughput of Zededra layers at sizes
-that resemble a real model's, beside the dense Llama-style decoder at equal size.
+"""``bench.py --design zededra | logulix``: prefill and decode throughput of the design's
+layers at sizes that resemble a real model's, beside the dense Llama-style decoder at equal
+size.
 
 Every model has random weights (N(0, 0.02^2), drawn on the device), ``--layers`` layers
 (default 4) and the same width, head count, head size, feed-forward width and bytes of
@@ -44,6 +45,36 @@ def zededra_config(s: dict, kind: str, layers: int, vocab: int = 32000) -> dict:
             "layers": [layer] * layers}
 
 
+def logulix_config(s: dict, kind: str, layers: int, vocab: int = 32000) -> dict:
+    """Layers of one kind of Logulix mixer with the ungated feed-forward: attention with the
+    dense decoder's heads (a window of 1,024, three taps, capped scores, full rotation), wkv
+    with heads of 64 and a decay of inner size 64, retention with keys of the head size and
+    values twice as long."""
+    kv = max(1, s["kv_rank"] // (2 * s["dim"]), s["heads"] // 16)
+    attention = {"type": "attention",
+                 "mixer": {"dim": s["dim"], "heads": s["heads"], "kv_heads": kv, "vdim": s["dim"],
+                           "scale": s["dim"] ** -0.5, "conv": 3, "softcap": 30.0,
+                           "mask": {"size": 1024},
+                           "rot": {"base": 10000.0, "dims": s["dim"], "scaling": {"factor": 8.0}}}}
+    wkv = {"type": "wkv", "mixer": {"dim": 64, "heads": s["width"] // 64, "rank": 64}}
+    heads = s["heads"]
+    retention = {"type": "retention",
+                 "mixer": {"dim": s["dim"], "heads": heads, "vdim": 2 * s["dim"],
+                           "decay": [1.0 - 2.0 ** (-5 - 3 * i / heads) for i in range(heads)],
+                           "rot": {"base": 1e6, "dims": s["dim"]}}}
+    dense = {"ff": s["ff"], "kind": "dense"}
+    layer = {"attention_dense": dict(attention, mlp=dense), "wkv_dense": dict(wkv, mlp=dense),
+             "retention_dense": dict(retention, mlp=dense)}[kind]
+    return {"architecture": "Logulix", "vocab": vocab, "width": s["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "logit_scale": 1.0, "layers": [layer] * layers}
+
+
+DESIGNS = {
+    "zededra": (zededra_config, ("latent_dense", "latent_moe", "mlstm_dense")),
+    "logulix": (logulix_config, ("attention_dense", "wkv_dense", "retention_dense")),
+}
+
+
 def llama_config(s: dict, layers: int, vocab: int = 32000) -> dict:
     # kv heads of the latent's size in keys plus values, i.e. the same cache bytes a token (but
     # at most 16 query heads a kv head, the most the fused decode attention takes)
@@ -57,8 +88,11 @@ def llama_config(s: dict, layers: int, vocab: int = 32000) -> dict:
 _LEAVES = ("embed", "add_rmsnorm", "gather_add_rmsnorm", "add_layernorm", "residual_add",
            "rope_store", "paged_attention", "attention_decode_fused", "swiglu", "clamped_glu",
            "latent_norm_store", "headwise_linear", "mlstm_scan", "mlstm_finish", "route",
-           "expert_glu", "expert_down", "expert_combine")
-_PRODUCTS = ("linear", "linear_parts", "linear_swiglu", "linear_clamped_glu")
+           "expert_glu", "expert_down", "expert_combine", "qk_conv_norm_rope_store",
+           "tail_update", "token_shift_mix", "linear_scan", "scan_finish", "rotate_rows",
+           "decay_lowrank", "relu_squared", "scale_", "settle_concat")
+_PRODUCTS = ("linear", "linear_parts", "linear_swiglu", "linear_clamped_glu",
+             "linear_relu_squared")
 
 
 class OpTimer:
@@ -196,16 +230,18 @@ def run(args, peaks: dict, peaks_source: str) -> dict:
     torch.cuda.set_device(0)
     layers = args.layers or 4
     sizes = [args.size] if args.size else list(SIZES)
-    result = {"metric": "zededra_layers_beside_llama_dense", "unit": "tokens/s", "layers": layers,
+    design = args.design
+    make_config, kinds = DESIGNS[design]
+    result = {"metric": f"{design}_layers_beside_llama_dense", "unit": "tokens/s", "layers": layers,
               "prompt_tokens": PROMPT, "decode_batch": BATCH, "decode_context": PROMPT,
               "dtype": "bf16", "data": "synthetic", "peaks": peaks, "peaks_source": peaks_source,
               "device": torch.cuda.get_device_name(0), "sizes": {}}
     for name in sizes:
         s = SIZES[name]
         rows = {"llama_dense": measure(torch, llama_config(s, layers), args.steps, args.warmup)}
-        for kind in ("latent_dense", "latent_moe", "mlstm_dense"):
-            rows[f"zededra_{kind}"] = measure(torch, zededra_config(s, kind, layers), args.steps,
-                                              args.warmup)
+        for kind in kinds:
+            rows[f"{design}_{kind}"] = measure(torch, make_config(s, kind, layers), args.steps,
+                                               args.warmup)
         result["sizes"][name] = rows
     return result
 

@@ -160,6 +160,17 @@ static __device__ __forceinline__ void rotate_half4(float4 x1, float4 x2, float4
     o2.w = __fadd_rn(__fmul_rn(x2.w, cs.w), __fmul_rn(x1.w, sn.w));
 }
 
+// Cosine and sine of position * freq: the product and its reduction to [-pi, pi] in
+// float64 (so that a position in the millions loses nothing), the functions themselves in
+// float32 on the reduced angle.
+static __device__ __forceinline__ void angle_cos_sin(int position, double freq, float& c,
+                                                     float& s) {
+    const double two_pi = 6.283185307179586476925286766559;
+    const double a = (double)position * freq;
+    const float r = (float)(a - two_pi * rint(a / two_pi));
+    sincosf(r, &s, &c);
+}
+
 // Streaming multiprocessors of the current device (148 on a B200), asked once.
 static inline int sm_count() {
     static const int n = [] {

@@ -14,12 +14,14 @@
 // thread (column, row group) keeps every eighth row of its column in registers, a warp holds
 // four columns times eight row groups, and the sum over i is the thread's rows in order
 // followed by three shuffles: the order never depends on the batch or on how the tokens
-// were cut into steps.  Tokens are taken 16 at a time through shared memory.
+// were cut into steps.  Tokens are taken 16 or 32 at a time through shared memory, four of
+// them side by side where only the state's own update has to wait for the token before.
 //
 //   mls_scan_finish      o / rms(o) per head (eps inside the root) * weight * silu(gate)
 //   mls_rotate_rows      rotation of the first `dims` entries of every head of q and k,
 //                        entry i paired with i + dims/2, k then times a constant; float32 out
 //   mls_decay_lowrank    w = exp(-exp(W2 tanh(lo) + w0)) from the low-rank pre-activation
+//                        (W2 handed over transposed)
 //
 // State, decays, exponentials, angles' cosines and sines, norms and sums are float32 (the
 // angles themselves float64: position * frequency); a, k, v come from the projections.
@@ -29,9 +31,21 @@ namespace {
 constexpr int LS_COLS = 16;         // columns of S a CTA owns
 constexpr int LS_GROUPS = 8;        // row groups: lanes that share a column
 constexpr int LS_THREADS = LS_COLS * LS_GROUPS;
-constexpr int LS_TOKENS = 16;       // tokens a pass
+constexpr int LS_UNROLL = 4;        // tokens whose sums over the row groups run side by side
 
-template <int RPT>
+// Four consecutive entries of a row as floats (the index a multiple of four, the row's start
+// aligned to 16 bytes).
+__device__ __forceinline__ float4 load4(const void* base, int dtype, size_t i) {
+    if (dtype == MLS_BF16) {
+        const uint2 raw = *reinterpret_cast<const uint2*>((const __nv_bfloat16*)base + i);
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(lo.x, lo.y, hi.x, hi.y);
+    }
+    return *reinterpret_cast<const float4*>((const float*)base + i);
+}
+
+template <int RPT, bool TOK_DECAY>
 __global__ void __launch_bounds__(LS_THREADS)
 linear_scan_kernel(const void* __restrict__ a_src, int a_dtype, int a_row, int a_off,
                    const void* __restrict__ k_src, int k_dtype, int k_row, int k_off,
@@ -41,7 +55,7 @@ linear_scan_kernel(const void* __restrict__ a_src, int a_dtype, int a_row, int a
                    const void* __restrict__ bonus, int bonus_dtype, int read_first,
                    const int* __restrict__ cu_q, const int* __restrict__ state_slot,
                    float* __restrict__ state, long long state_stride,
-                   int n_heads, int e, int f, float* __restrict__ out) {
+                   int n_heads, int e, int f, int tokens_a_pass, float* __restrict__ out) {
     chain_release();
     chain_wait();
     const int r = blockIdx.z, head = blockIdx.y, col0 = blockIdx.x * LS_COLS;
@@ -49,13 +63,11 @@ linear_scan_kernel(const void* __restrict__ a_src, int a_dtype, int a_row, int a
     if (n <= 0) return;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int grp = lane & (LS_GROUPS - 1);               // row group: the low three lane bits
-    const int col = col0 + warp * 4 + (lane >> 3);
+    const int my_col = warp * 4 + (lane >> 3);
+    const int col = col0 + my_col;
     const bool col_ok = col < f;
-    extern __shared__ float smem[];
-    float* a_s = smem;                                    // [LS_TOKENS][e]
-    float* k_s = a_s + LS_TOKENS * e;
-    float* w_s = k_s + LS_TOKENS * e;                     // decays per key channel (read first)
-    float* v_s = w_s + (decay_tok ? LS_TOKENS * e : 0);   // [LS_TOKENS][LS_COLS]
+    extern __shared__ float4 akw_s[];                     // [tokens][e]: (a, k, decay, -)
+    float* v_s = reinterpret_cast<float*>(akw_s + (size_t)tokens_a_pass * e);   // [tokens][LS_COLS]
 
     float* S = state + (size_t)state_slot[r] * state_stride + (size_t)head * e * f;
     float s[RPT], ub[RPT];
@@ -65,54 +77,118 @@ linear_scan_kernel(const void* __restrict__ a_src, int a_dtype, int a_row, int a
         s[i] = (col_ok && row < e) ? S[(size_t)row * f + col] : 0.f;
         ub[i] = (bonus && row < e) ? load_as_float(bonus, (size_t)head * e + row, bonus_dtype) : 0.f;
     }
-    const float g = decay_head ? decay_head[head] : 1.f;
+    const float g = TOK_DECAY ? 1.f : decay_head[head];
+    // whether every row of a, k, v and the decays can be read four entries at a time
+    const bool vec4 = ((e | f | a_row | a_off | k_row | k_off | v_row | v_off) & 3) == 0 &&
+                      (!TOK_DECAY || (decay_row & 3) == 0);
+    float* out_col = out + (size_t)head * f + col;
+    const size_t out_row = (size_t)n_heads * f;
 
-    for (int b0 = 0; b0 < n; b0 += LS_TOKENS) {
-        const int nb = min(LS_TOKENS, n - b0);
+    for (int b0 = 0; b0 < n; b0 += tokens_a_pass) {
+        const int nb = min(tokens_a_pass, n - b0);
         __syncthreads();
-        for (int u = threadIdx.x; u < nb * e; u += LS_THREADS) {
-            const int tt = u / e, i = u - tt * e;
-            const size_t t = (size_t)(t0 + b0 + tt);
-            a_s[u] = load_as_float(a_src, t * a_row + a_off + head * e + i, a_dtype);
-            k_s[u] = load_as_float(k_src, t * k_row + k_off + head * e + i, k_dtype);
-            if (decay_tok) w_s[u] = decay_tok[t * decay_row + head * e + i];
-        }
-        for (int u = threadIdx.x; u < nb * LS_COLS; u += LS_THREADS) {
-            const int tt = u / LS_COLS, j = u - tt * LS_COLS;
-            const size_t t = (size_t)(t0 + b0 + tt);
-            v_s[u] = col0 + j < f
-                ? load_as_float(v_src, t * v_row + v_off + head * f + col0 + j, v_dtype) : 0.f;
-        }
-        __syncthreads();
-        for (int tt = 0; tt < nb; ++tt) {
-            const float vj = v_s[tt * LS_COLS + warp * 4 + (lane >> 3)];
-            const float* at = a_s + tt * e + grp;
-            const float* kt = k_s + tt * e + grp;
-            const float* wt = w_s + tt * e + grp;
-            float acc = 0.f;
-            if (read_first) {
+        if (vec4) {
+            // four consecutive entries a load, two such units a thread under way at a time
+            const int e4 = e >> 2, units = nb * e4;
+            for (int u0 = threadIdx.x; u0 < units; u0 += 2 * LS_THREADS) {
+                float4 av[2], kv[2], wv[2];
+                int at[2];
 #pragma unroll
-                for (int i = 0; i < RPT; ++i) {
-                    if (i * LS_GROUPS + grp < e) {
-                        const float ki = kt[i * LS_GROUPS];
-                        acc = fmaf(at[i * LS_GROUPS], fmaf(ub[i] * ki, vj, s[i]), acc);
-                        s[i] = fmaf(decay_tok ? wt[i * LS_GROUPS] : g, s[i], ki * vj);
+                for (int j = 0; j < 2; ++j) {
+                    const int u = u0 + j * LS_THREADS;
+                    at[j] = -1;
+                    if (u < units) {
+                        const int tt = u / e4, i = (u - tt * e4) << 2;
+                        const size_t t = (size_t)(t0 + b0 + tt);
+                        av[j] = load4(a_src, a_dtype, t * a_row + a_off + head * e + i);
+                        kv[j] = load4(k_src, k_dtype, t * k_row + k_off + head * e + i);
+                        wv[j] = TOK_DECAY ? *reinterpret_cast<const float4*>(
+                                                decay_tok + t * decay_row + head * e + i)
+                                          : make_float4(g, g, g, g);
+                        at[j] = tt * e + i;
                     }
                 }
-            } else {
 #pragma unroll
-                for (int i = 0; i < RPT; ++i) {
-                    if (i * LS_GROUPS + grp < e) {
-                        s[i] = fmaf(decay_tok ? wt[i * LS_GROUPS] : g, s[i], kt[i * LS_GROUPS] * vj);
-                        acc = fmaf(at[i * LS_GROUPS], s[i], acc);
+                for (int j = 0; j < 2; ++j) {
+                    if (at[j] >= 0) {
+                        float4* dst = akw_s + at[j];
+                        dst[0] = make_float4(av[j].x, kv[j].x, wv[j].x, 0.f);
+                        dst[1] = make_float4(av[j].y, kv[j].y, wv[j].y, 0.f);
+                        dst[2] = make_float4(av[j].z, kv[j].z, wv[j].z, 0.f);
+                        dst[3] = make_float4(av[j].w, kv[j].w, wv[j].w, 0.f);
                     }
                 }
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-            if (grp == 0 && col_ok)
-                out[(size_t)(t0 + b0 + tt) * n_heads * f + (size_t)head * f + col] = acc;
+            for (int u = threadIdx.x; u < nb * (LS_COLS / 4); u += LS_THREADS) {
+                const int tt = u / (LS_COLS / 4), j = (u - tt * (LS_COLS / 4)) << 2;
+                const size_t t = (size_t)(t0 + b0 + tt);
+                float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (col0 + j < f)                      // f is a multiple of four here
+                    x = load4(v_src, v_dtype, t * v_row + v_off + head * f + col0 + j);
+                *reinterpret_cast<float4*>(v_s + tt * LS_COLS + j) = x;
+            }
+        } else {
+            for (int u = threadIdx.x; u < nb * e; u += LS_THREADS) {
+                const int tt = u / e, i = u - tt * e;
+                const size_t t = (size_t)(t0 + b0 + tt);
+                float4 x;
+                x.x = load_as_float(a_src, t * a_row + a_off + head * e + i, a_dtype);
+                x.y = load_as_float(k_src, t * k_row + k_off + head * e + i, k_dtype);
+                x.z = TOK_DECAY ? decay_tok[t * decay_row + head * e + i] : g;
+                x.w = 0.f;
+                akw_s[u] = x;
+            }
+            for (int u = threadIdx.x; u < nb * LS_COLS; u += LS_THREADS) {
+                const int tt = u / LS_COLS, j = u - tt * LS_COLS;
+                const size_t t = (size_t)(t0 + b0 + tt);
+                v_s[u] = col0 + j < f
+                    ? load_as_float(v_src, t * v_row + v_off + head * f + col0 + j, v_dtype) : 0.f;
+            }
+        }
+        __syncthreads();
+        // LS_UNROLL tokens at a time: their sums over the row groups (three shuffles each)
+        // run side by side, only the state's own chain is sequential
+        for (int tt0 = 0; tt0 < nb; tt0 += LS_UNROLL) {
+            float acc[LS_UNROLL];
+#pragma unroll
+            for (int u = 0; u < LS_UNROLL; ++u) {
+                acc[u] = 0.f;
+                const int tt = tt0 + u;
+                if (tt < nb) {
+                    const float vj = v_s[tt * LS_COLS + my_col];
+                    const float4* row = akw_s + (size_t)tt * e + grp;
+                    if (read_first) {
+#pragma unroll
+                        for (int i = 0; i < RPT; ++i) {
+                            if (i * LS_GROUPS + grp < e) {
+                                const float4 x = row[i * LS_GROUPS];
+                                acc[u] = fmaf(x.x, fmaf(ub[i] * x.y, vj, s[i]), acc[u]);
+                                s[i] = fmaf(x.z, s[i], x.y * vj);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < RPT; ++i) {
+                            if (i * LS_GROUPS + grp < e) {
+                                const float4 x = row[i * LS_GROUPS];
+                                s[i] = fmaf(x.z, s[i], x.y * vj);
+                                acc[u] = fmaf(x.x, s[i], acc[u]);
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < LS_UNROLL; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], 1);
+#pragma unroll
+            for (int u = 0; u < LS_UNROLL; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], 2);
+#pragma unroll
+            for (int u = 0; u < LS_UNROLL; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], 4);
+            if (grp == 0 && col_ok) {
+#pragma unroll
+                for (int u = 0; u < LS_UNROLL; ++u)
+                    if (tt0 + u < nb) out_col[(size_t)(t0 + b0 + tt0 + u) * out_row] = acc[u];
+            }
         }
     }
 #pragma unroll
@@ -158,12 +234,8 @@ rotate_rows_kernel(const T* __restrict__ src, int src_row, int q_off, int k_off,
     const int t = blockIdx.x, half = dims / 2;
     chain_wait();
     const int p = positions[t];
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        double s, c;
-        sincos((double)p * freq[i], &s, &c);
-        cs[i] = (float)c;
-        cs[half + i] = (float)s;
-    }
+    for (int i = threadIdx.x; i < half; i += blockDim.x)
+        angle_cos_sin(p, freq[i], cs[i], cs[half + i]);
     __syncthreads();
     const int width = n_heads * e;
     for (int u = threadIdx.x; u < 2 * width; u += blockDim.x) {
@@ -181,24 +253,37 @@ rotate_rows_kernel(const T* __restrict__ src, int src_row, int q_off, int k_off,
     }
 }
 
-// One block a token: lo (float32 [T, rank], before its tanh) -> w [T, channels].
+// lo (float32 [T, rank], before its tanh) -> w [T, channels].  A block takes DL_TOKENS tokens
+// and 256 channels: tanh(lo) of its tokens lies in shared memory, a thread owns one channel
+// and reads its column of W2 (handed over transposed, [rank, channels], so that a warp reads
+// consecutive floats) once for all its tokens.  k ascending: a token's sum does not depend
+// on its block.
+constexpr int DL_TOKENS = 16;
 __global__ void __launch_bounds__(256)
-decay_lowrank_kernel(const float* __restrict__ lo, int rank, const float* __restrict__ w2,
+decay_lowrank_kernel(const float* __restrict__ lo, int rank, const float* __restrict__ w2t,
                      const void* __restrict__ w0, int w0_dtype, float* __restrict__ out,
-                     int channels) {
+                     int n_tokens, int channels) {
     chain_release();
-    extern __shared__ float th[];                        // [rank]
+    extern __shared__ float th[];                        // [DL_TOKENS][rank]
+    const int t0 = blockIdx.y * DL_TOKENS, nt = min(DL_TOKENS, n_tokens - t0);
+    const int c = blockIdx.x * 256 + threadIdx.x;
     chain_wait();
-    const int t = blockIdx.x;
-    for (int i = threadIdx.x; i < rank; i += blockDim.x) th[i] = tanhf(lo[(size_t)t * rank + i]);
+    for (int u = threadIdx.x; u < nt * rank; u += 256) th[u] = tanhf(lo[(size_t)t0 * rank + u]);
     __syncthreads();
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-        const float* wr = w2 + (size_t)c * rank;
-        float z = 0.f;
-        for (int i = 0; i < rank; ++i) z = fmaf(wr[i], th[i], z);
-        z += load_as_float(w0, c, w0_dtype);
-        out[(size_t)t * channels + c] = expf(-expf(z));
+    if (c >= channels) return;
+    float z[DL_TOKENS];
+#pragma unroll
+    for (int tt = 0; tt < DL_TOKENS; ++tt) z[tt] = 0.f;
+    for (int i = 0; i < rank; ++i) {
+        const float w = w2t[(size_t)i * channels + c];
+#pragma unroll
+        for (int tt = 0; tt < DL_TOKENS; ++tt)
+            if (tt < nt) z[tt] = fmaf(w, th[tt * rank + i], z[tt]);
     }
+    const float b = load_as_float(w0, c, w0_dtype);
+#pragma unroll
+    for (int tt = 0; tt < DL_TOKENS; ++tt)
+        if (tt < nt) out[(size_t)(t0 + tt) * channels + c] = expf(-expf(z[tt] + b));
 }
 
 template <int RPT>
@@ -207,8 +292,8 @@ int launch_scan(dim3 grid, size_t smem, cudaStream_t stream, const void* a_src, 
                 const void* v_src, int v_dtype, int v_row, int v_off, const float* decay_tok,
                 int decay_row, const float* decay_head, const void* bonus, int bonus_dtype,
                 int read_first, const int* cu_q, const int* state_slot, float* state,
-                long long state_stride, int n_heads, int e, int f, float* out) {
-    auto kernel = linear_scan_kernel<RPT>;
+                long long state_stride, int n_heads, int e, int f, int tokens_a_pass, float* out) {
+    auto kernel = decay_tok ? linear_scan_kernel<RPT, true> : linear_scan_kernel<RPT, false>;
     if (smem > 48 * 1024) {
         const int rc = (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                  (int)smem);
@@ -217,7 +302,7 @@ int launch_scan(dim3 grid, size_t smem, cudaStream_t stream, const void* a_src, 
     MLS_LAUNCH(kernel, grid, dim3(LS_THREADS), smem, stream, a_src, a_dtype, a_row, a_off, k_src,
                k_dtype, k_row, k_off, v_src, v_dtype, v_row, v_off, decay_tok, decay_row,
                decay_head, bonus, bonus_dtype, read_first, cu_q, state_slot, state, state_stride,
-               n_heads, e, f, out);
+               n_heads, e, f, tokens_a_pass, out);
     return launch_status();
 }
 }  // namespace
@@ -234,13 +319,14 @@ MLS_API int mls_linear_scan(const void* a_src, int a_dtype, int a_row, int a_off
     if (e <= 0 || f <= 0 || e > 32 * LS_GROUPS || (!decay_tok == !decay_head))
         return MLS_ERR_UNSUPPORTED;
     const dim3 grid((f + LS_COLS - 1) / LS_COLS, n_heads, n_requests);
-    const size_t smem = (size_t)LS_TOKENS * ((decay_tok ? 3 : 2) * e + LS_COLS) * sizeof(float);
+    const int tokens_a_pass = e <= 64 ? 32 : 16;
+    const size_t smem = (size_t)tokens_a_pass * (e * sizeof(float4) + LS_COLS * sizeof(float));
     const int rpt = (e + LS_GROUPS - 1) / LS_GROUPS;
 #define LS_GO(R)                                                                                 \
     return launch_scan<R>(grid, smem, stream, a_src, a_dtype, a_row, a_off, k_src, k_dtype, k_row, \
                           k_off, v_src, v_dtype, v_row, v_off, decay_tok, decay_row, decay_head,  \
                           bonus, bonus_dtype, read_first, cu_q, state_slot, state, state_stride,  \
-                          n_heads, e, f, out)
+                          n_heads, e, f, tokens_a_pass, out)
     if (rpt <= 2) LS_GO(2);
     if (rpt <= 4) LS_GO(4);
     if (rpt <= 8) LS_GO(8);
@@ -284,13 +370,14 @@ MLS_API int mls_rotate_rows(const void* src, int src_dtype, int src_row, int q_o
     return launch_status();
 }
 
-MLS_API int mls_decay_lowrank(const float* lo, int rank, const float* w2, const void* w0,
+MLS_API int mls_decay_lowrank(const float* lo, int rank, const float* w2t, const void* w0,
                               int w0_dtype, float* out, int n_tokens, int channels,
                               cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    const size_t smem = (size_t)rank * sizeof(float);
+    const size_t smem = (size_t)DL_TOKENS * rank * sizeof(float);
     if (rank <= 0 || smem > 48 * 1024) return MLS_ERR_UNSUPPORTED;
-    MLS_LAUNCH((decay_lowrank_kernel), dim3(n_tokens), dim3(256), smem, stream, lo, rank, w2, w0,
-               w0_dtype, out, channels);
+    const dim3 grid((channels + 255) / 256, (n_tokens + DL_TOKENS - 1) / DL_TOKENS);
+    MLS_LAUNCH((decay_lowrank_kernel), grid, dim3(256), smem, stream, lo, rank, w2t, w0, w0_dtype,
+               out, n_tokens, channels);
     return launch_status();
 }

@@ -18,8 +18,8 @@
 //   mls_tail_update               tail := the last taps - 1 inputs after this step
 //
 // Angles are formed in float64 (position * frequency, frequencies handed over as
-// float64) and their cosine and sine rounded once to float32; sums, norms and the
-// rotation are float32.
+// float64) and brought into [-pi, pi] there; their cosine and sine are float32, as are
+// sums, norms and the rotation.
 #include "common.cuh"
 #include "page_tail.cuh"
 
@@ -66,12 +66,8 @@ qk_conv_norm_rope_store_kernel(
     const int r = req_of_token[t], row0 = cu_q[r], i_t = t - row0, p = positions[t];
     const int n_tail = taps - 1;
     const float* my_tail = n_tail > 0 ? tail + (size_t)state_slot[r] * tail_stride : nullptr;
-    if (threadIdx.x < rot_dims / 2) {
-        double s, c;
-        sincos((double)p * freq[threadIdx.x], &s, &c);
-        cs[threadIdx.x] = (float)c;
-        cs[rot_dims / 2 + threadIdx.x] = (float)s;
-    }
+    if (threadIdx.x < rot_dims / 2)
+        angle_cos_sin(p, freq[threadIdx.x], cs[threadIdx.x], cs[rot_dims / 2 + threadIdx.x]);
     float ssq = 0.f, ssk = 0.f;
     for (int c = threadIdx.x; c < channels; c += SC_THREADS) {
         float acc;

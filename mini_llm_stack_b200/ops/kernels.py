@@ -1050,6 +1050,10 @@ class Ops:
             _ptr(step.state_slot), _ptr(step.cu_q), _ptr(step.req_of_token), _ptr(out),
             _ptr(out_f32), t, d, self._stream()), "token_shift_mix")
 
+    def require_scan(self, e: int) -> None:
+        """Say at bind time whether the scan kernel takes a key size."""
+        _need(0 < e <= 256, f"the scan kernel keeps up to 256 rows of a head's state, not {e}")
+
     def linear_scan(self, a, k, v, state, step, n_heads: int, e: int, f: int, out,
                     decay_tok=None, decay_head=None, bonus=None, read_first: bool = False) -> None:
         """Walk every request's tokens through the matrix state ``S [e, f]`` of every head.
@@ -1114,17 +1118,18 @@ class Ops:
             _ptr(freq) if dims else None, dims, float(k_scale), _ptr(out), t, n_heads, e,
             self._stream()), "rotate_rows")
 
-    def decay_lowrank(self, lo, w2, w0, out) -> None:
-        """``out = exp(-exp(tanh(lo) @ w2^T + w0))``, all float32."""
+    def decay_lowrank(self, lo, w2t, w0, out) -> None:
+        """``out = exp(-exp(tanh(lo) @ w2t + w0))``, all float32; ``w2t [rank, C]`` is the
+        second matrix of the decay transposed."""
         t, rank = lo.shape
-        c = w2.shape[0]
-        _need(lo.dtype == torch.float32 and lo.is_contiguous() and w2.shape == (c, rank)
-              and w2.dtype == torch.float32 and w2.is_contiguous() and w0.shape == (c,)
+        c = w2t.shape[1]
+        _need(lo.dtype == torch.float32 and lo.is_contiguous() and w2t.shape == (rank, c)
+              and w2t.dtype == torch.float32 and w2t.is_contiguous() and w0.shape == (c,)
               and out.shape == (t, c) and out.dtype == torch.float32 and out.is_contiguous(),
               "decay_lowrank: operands")
         self.launches += 1
         _check(self._part_lib("scan")["decay"](
-            _ptr(lo), rank, _ptr(w2), _ptr(w0), _code(w0.dtype), _ptr(out), t, c, self._stream()),
+            _ptr(lo), rank, _ptr(w2t), _ptr(w0), _code(w0.dtype), _ptr(out), t, c, self._stream()),
             "decay_lowrank")
 
     def sample(self, logits, temperature, uniform, out) -> None:

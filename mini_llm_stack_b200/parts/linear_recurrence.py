@@ -31,6 +31,7 @@ from .base import CacheHandle, FixedState, Mixer, StepContext, TensorSpec
 class WkvMixer(Mixer):
     decode_capturable = prompt_capturable = True   # forward only launches kernels on the current stream
     MIXES = ("r", "k", "v", "g", "w")
+    STACK_ROWS = 64       # up to so many rows (four a token) the four projections run as one product
 
     def __init__(self, d_model: int, n_heads: int, head_dim: int, decay_rank: int, eps: float):
         self.d_model, self.n_heads, self.head_dim = int(d_model), int(n_heads), int(head_dim)
@@ -63,11 +64,15 @@ class WkvMixer(Mixer):
         ops = runtime.ops
         ops.require_part("shortconv")
         ops.require_part("scan")
+        ops.require_scan(self.head_dim)
         self.mu = torch.stack([tensors[f"mu.{s}"] for s in self.MIXES]).contiguous()
-        self.w_rkvg = [ops.prepare_weight(tensors[s]) for s in ("r", "k", "v", "g")]
+        # the four projections stacked: each alone is a run of its rows
+        c = self.inner
+        self.w_all = ops.prepare_weight(torch.cat([tensors[s] for s in ("r", "k", "v", "g")], dim=0))
+        self.w_rkvg = [self.w_all[i * c:(i + 1) * c] for i in range(4)]
         # the decay is float32 from its mix to its exponentials
         self.w1 = tensors["w1"].float().contiguous()
-        self.w2 = tensors["w2"].float().contiguous()
+        self.w2t = tensors["w2"].float().t().contiguous()       # [rank, channels]
         self.w0 = tensors["w0"].contiguous()
         self.u = tensors["u"].contiguous()
         self.g_norm = tensors["norm"].contiguous()
@@ -82,18 +87,26 @@ class WkvMixer(Mixer):
         mix_w = rt.buffer("wkv_mix_w", (t, d), torch.float32)
         ops.token_shift_mix(h, self.mu, prev, mixes, mix_w, step)
         ops.tail_update(h, 0, d, None, prev, 1, step)
-        rkvg = rt.buffer("wkv_rkvg", (4, t, c), rt.act_dtype)
-        for i, w in enumerate(self.w_rkvg):
-            ops.linear(mixes[i], w, rkvg[i])
+        if 4 * t <= self.STACK_ROWS and self.w_all.dtype == torch.bfloat16:
+            # few tokens: the step streams weights, so one product of all four mixes with
+            # all four matrices (of whose sixteen blocks four are wanted) beats four products
+            both = rt.buffer("wkv_rkvg_all", (4 * t, 4 * c), rt.act_dtype)
+            ops.linear(mixes.view(4 * t, d), self.w_all, both)
+            r, k, v, gate = ((both[i * t:(i + 1) * t], i * c) for i in range(4))
+        else:
+            rkvg = rt.buffer("wkv_rkvg", (4, t, c), rt.act_dtype)
+            for i, w in enumerate(self.w_rkvg):
+                ops.linear(mixes[i], w, rkvg[i])
+            r, k, v, gate = ((rkvg[i], 0) for i in range(4))
         lo = rt.buffer("wkv_lo", (t, self.decay_rank), torch.float32)
         ops.linear(mix_w, self.w1, lo)
         decay = rt.buffer("wkv_decay", (t, c), torch.float32)
-        ops.decay_lowrank(lo, self.w2, self.w0, decay)
+        ops.decay_lowrank(lo, self.w2t, self.w0, decay)
         o = rt.buffer("scan_out", (t, c), torch.float32)
-        ops.linear_scan((rkvg[0], 0), (rkvg[1], 0), (rkvg[2], 0), cache.state, step, nh, e, e, o,
-                        decay_tok=decay, bonus=self.u, read_first=True)
+        ops.linear_scan(r, k, v, cache.state, step, nh, e, e, o, decay_tok=decay, bonus=self.u,
+                        read_first=True)
         y = rt.buffer("attn_out", (t, c), rt.act_dtype)
-        ops.scan_finish(o, rkvg[3], 0, self.g_norm, self.eps, y, nh, e)
+        ops.scan_finish(o, gate[0], gate[1], self.g_norm, self.eps, y, nh, e)
         delta = rt.buffer("delta", (t, d), rt.act_dtype)
         return ops.linear_parts(y, self.w_o, delta)
 
@@ -125,6 +138,7 @@ class RetentionMixer(Mixer):
         self.runtime = runtime
         ops = runtime.ops
         ops.require_part("scan")
+        ops.require_scan(self.qk_dim)
         self.w_qkvg = ops.prepare_weight(torch.cat(
             [tensors["q"], tensors["k"], tensors["v"], tensors["g"]], dim=0))
         self.w_o = ops.prepare_weight(tensors["o"])

@@ -43,3 +43,10 @@ def test_design_option_builds_layers_of_equal_size():
         latent = mod.zededra_config(s, "latent_dense", 2)["layers"][0]
         assert latent["mixer"]["heads"] == dense.n_heads and latent["mlp"]["ff"] == dense.intermediate_size
         assert 2 * dense.n_kv_heads * dense.head_dim >= latent["mixer"]["kv_rank"]
+        for kind in mod.DESIGNS["logulix"][1]:
+            g = config_from_dict(mod.logulix_config(s, kind, 2))
+            assert g.width == dense.d_model and len(g.layers) == dense.n_layers
+            assert g.layers[0]["mlp"]["ff"] == dense.intermediate_size
+        att = mod.logulix_config(s, "attention_dense", 2)["layers"][0]["mixer"]
+        assert (att["heads"], att["kv_heads"], att["dim"]) == (dense.n_heads, dense.n_kv_heads,
+                                                               dense.head_dim)

@@ -353,6 +353,9 @@ ONE_LAYER = {
     "attention_head_80": {"type": "attention", "mlp": None,
                           "mixer": L.attention(2, 1, 80, 0.1, conv=3, window=33,
                                                rot=L.rot(80, 10000.0), softcap=15.0)},
+    "attention_head_128": {"type": "attention", "mlp": None,
+                           "mixer": L.attention(2, 1, 128, 0.09, conv=2, window=50,
+                                                rot=L.rot(64, 10000.0, 8.0), softcap=30.0)},
     "wkv": {"type": "wkv", "mixer": L.wkv(2, 12, 6), "mlp": None},
     "wkv_one_head_rank1": {"type": "wkv", "mixer": L.wkv(1, 40, 1), "mlp": None},
     "retention": {"type": "retention", "mlp": None,
