@@ -126,6 +126,151 @@ qk_conv_norm_rope_store_kernel(
         clear_page_tail<T>(rest, slot, block_size, (int)n_pages, n_kv, hd, k_pool, v_pool);
 }
 
+// The same with four consecutive channels a thread and step (channels, query channels and
+// the head size multiples of four): 16-byte loads of the projection's rows, the taps and
+// norm weights of four channels at once, and a rotation whose pairs (2i, 2i + 1) lie inside
+// the thread's four values.  The sums run in another order than in the kernel above, so a
+// model takes one of the two for all its steps (the choice depends on its sizes alone).
+struct Four { float v[4]; };
+__device__ __forceinline__ Four load_four(const void* base, size_t i, int dtype) {
+    Four r;
+    if (dtype == MLS_BF16) {
+        const uint2 raw = *reinterpret_cast<const uint2*>((const __nv_bfloat16*)base + i);
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        r.v[0] = lo.x; r.v[1] = lo.y; r.v[2] = hi.x; r.v[3] = hi.y;
+    } else {
+        const float4 x = *reinterpret_cast<const float4*>((const float*)base + i);
+        r.v[0] = x.x; r.v[1] = x.y; r.v[2] = x.z; r.v[3] = x.w;
+    }
+    return r;
+}
+template <typename T>
+__device__ __forceinline__ void store_four(T* dst, const float (&v)[4]);
+template <>
+__device__ __forceinline__ void store_four<float>(float* dst, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <>
+__device__ __forceinline__ void store_four<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[4]) {
+    *reinterpret_cast<uint2*>(dst) = pack_bf16x4(make_float4(v[0], v[1], v[2], v[3]));
+}
+
+constexpr int QK_MAX_TAPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(SC_THREADS)
+qk_conv_norm_rope_store_vec4_kernel(
+        const float* __restrict__ proj, const void* __restrict__ bias,
+        const void* __restrict__ conv_w, int taps, const void* __restrict__ q_norm,
+        const void* __restrict__ k_norm, int w_dtype, float eps,
+        const float* __restrict__ tail, long long tail_stride,
+        const int* __restrict__ state_slot, const int* __restrict__ cu_q,
+        const int* __restrict__ req_of_token, const int* __restrict__ positions,
+        const double* __restrict__ freq, int rot_dims,
+        T* __restrict__ q_out, int q_row, const int* __restrict__ slot_map,
+        T* __restrict__ k_pool, T* __restrict__ v_pool, int block_size, long long pool_slots,
+        int n_tokens, int n_heads, int n_kv, int hd, int writes, int* status) {
+    chain_release();
+    extern __shared__ float smem[];
+    const int cq = n_heads * hd, ck = n_kv * hd, channels = cq + ck, half = rot_dims / 2;
+    float* y = smem;                       // [channels] convolved
+    float* cs = y + channels;              // [rot_dims]: cos | sin
+    __shared__ float sums[SC_THREADS / 32][2];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int slot = writes ? slot_map[t] : -1;
+    const int rest = writes ? page_tail_to_clear(slot_map, t, n_tokens, slot, block_size) : 0;
+    chain_wait();
+    const int r = req_of_token[t], i_t = t - cu_q[r], p = positions[t];
+    const int n_tail = taps > 0 ? taps - 1 : 0;
+    const float* my_tail = n_tail > 0 ? tail + (size_t)state_slot[r] * tail_stride : nullptr;
+    if (threadIdx.x < half)
+        angle_cos_sin(p, freq[threadIdx.x], cs[threadIdx.x], cs[half + threadIdx.x]);
+    float ssq = 0.f, ssk = 0.f;
+    for (int c = threadIdx.x * 4; c < channels; c += blockDim.x * 4) {
+        Four b;
+        b.v[0] = b.v[1] = b.v[2] = b.v[3] = 0.f;
+        if (bias) b = load_four(bias, c, w_dtype);
+        float acc[4];
+        if (taps == 0) {
+            const float4 x = *reinterpret_cast<const float4*>(proj + (size_t)t * channels + c);
+            acc[0] = x.x + b.v[0]; acc[1] = x.y + b.v[1]; acc[2] = x.z + b.v[2]; acc[3] = x.w + b.v[3];
+        } else {
+            acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+#pragma unroll
+            for (int j = 0; j < QK_MAX_TAPS; ++j) {
+                if (j < taps) {
+                    const int i = i_t - n_tail + j;
+                    float4 x;
+                    if (i >= 0) {
+                        x = *reinterpret_cast<const float4*>(proj + (size_t)(t - n_tail + j) * channels + c);
+                        x.x += b.v[0]; x.y += b.v[1]; x.z += b.v[2]; x.w += b.v[3];
+                    } else {
+                        x = *reinterpret_cast<const float4*>(my_tail + (size_t)(n_tail + i) * channels + c);
+                    }
+                    const size_t wj = (size_t)c * taps + j;          // [channel][tap]
+                    acc[0] = fmaf(load_as_float(conv_w, wj, w_dtype), x.x, acc[0]);
+                    acc[1] = fmaf(load_as_float(conv_w, wj + taps, w_dtype), x.y, acc[1]);
+                    acc[2] = fmaf(load_as_float(conv_w, wj + 2 * taps, w_dtype), x.z, acc[2]);
+                    acc[3] = fmaf(load_as_float(conv_w, wj + 3 * taps, w_dtype), x.w, acc[3]);
+                }
+            }
+        }
+        *reinterpret_cast<float4*>(y + c) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        const float s4 = fmaf(acc[0], acc[0], fmaf(acc[1], acc[1], fmaf(acc[2], acc[2], acc[3] * acc[3])));
+        if (c < cq) ssq += s4; else ssk += s4;
+    }
+    const bool slot_ok = slot >= 0 && slot < pool_slots;
+    if (writes && !slot_ok && threadIdx.x == 0) atomicOr(status, MLS_STATUS_BAD_SLOT);
+    ssq = warp_sum(ssq);
+    ssk = warp_sum(ssk);
+    if (lane == 0) {
+        sums[warp][0] = ssq;
+        sums[warp][1] = ssk;
+    }
+    __syncthreads();
+    float tq = 0.f, tk = 0.f;
+    for (int wv = 0; wv < (int)(blockDim.x >> 5); ++wv) {       // warps in order
+        tq += sums[wv][0];
+        tk += sums[wv][1];
+    }
+    const float inv_q = 1.0f / sqrtf(tq / (float)cq + eps);
+    const float inv_k = 1.0f / sqrtf(tk / (float)ck + eps);
+    const long long page = slot_ok ? slot / block_size : 0;
+    const int off = slot_ok ? slot % block_size : 0;
+    const long long n_pages = pool_slots / block_size;
+    for (int c = threadIdx.x * 4; c < channels; c += blockDim.x * 4) {
+        const bool is_q = c < cq;
+        const int cc = is_q ? c : c - cq;
+        const int e = cc % hd, g = cc / hd;
+        const float inv = is_q ? inv_q : inv_k;
+        const float4 raw4 = *reinterpret_cast<const float4*>(y + c);
+        const float raw[4] = {raw4.x, raw4.y, raw4.z, raw4.w};
+        const Four nw = load_four(is_q ? q_norm : k_norm, cc, w_dtype);
+        float v[4];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) v[q4] = raw[q4] * inv * nw.v[q4];
+#pragma unroll
+        for (int pr = 0; pr < 2; ++pr) {
+            if (e + 2 * pr < rot_dims) {
+                const float co = cs[(e >> 1) + pr], si = cs[half + (e >> 1) + pr];
+                const float a = v[2 * pr], bb = v[2 * pr + 1];
+                v[2 * pr] = __fsub_rn(__fmul_rn(a, co), __fmul_rn(bb, si));
+                v[2 * pr + 1] = __fadd_rn(__fmul_rn(bb, co), __fmul_rn(a, si));
+            }
+        }
+        if (is_q) {
+            store_four<T>(q_out + (size_t)t * q_row + c, v);
+        } else if (writes && slot_ok) {
+            const size_t at = (((size_t)g * n_pages + page) * block_size + off) * hd + e;
+            store_four<T>(k_pool + at, v);
+            store_four<T>(v_pool + at, raw);           // the value: the convolved key as it is
+        }
+    }
+    if (writes && slot_ok)
+        clear_page_tail<T>(rest, slot, block_size, (int)n_pages, n_kv, hd, k_pool, v_pool);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(SC_THREADS)
 token_shift_mix_kernel(const T* __restrict__ h, const void* __restrict__ mu, int w_dtype,
@@ -193,31 +338,38 @@ MLS_API int mls_qk_conv_norm_rope_store(
         int n_tokens, int n_heads, int n_kv, int hd, int writes, int* status,
         cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (taps < 0 || (taps > 1 && !tail) || rot_dims < 0 || rot_dims > hd || (rot_dims & 1) ||
+    if (taps < 0 || taps > QK_MAX_TAPS || (taps > 1 && !tail) || rot_dims < 0 || rot_dims > hd || (rot_dims & 1) ||
         rot_dims / 2 > SC_THREADS || (rot_dims > 0 && !freq))
         return MLS_ERR_UNSUPPORTED;
     const size_t smem = ((size_t)(n_heads + n_kv) * hd + rot_dims) * sizeof(float);
     if (smem > 200 * 1024) return MLS_ERR_UNSUPPORTED;
+    // four channels a thread where every row allows it (the model's sizes alone decide)
+    const bool vec4 = (((n_heads * hd) | hd | q_row) & 3) == 0 &&
+                      (taps <= 1 || (tail_stride & 3) == 0);
+    // (the block's shape depends on the model's sizes alone, and with it the order of the sums)
+    const int threads = (vec4 && (n_heads + n_kv) * hd <= 4096 && rot_dims / 2 <= 128) ? 128 : SC_THREADS;
     if (act_dtype == MLS_BF16) {
-        auto kernel = qk_conv_norm_rope_store_kernel<__nv_bfloat16>;
+        auto kernel = vec4 ? qk_conv_norm_rope_store_vec4_kernel<__nv_bfloat16>
+                           : qk_conv_norm_rope_store_kernel<__nv_bfloat16>;
         if (smem > 48 * 1024) {
             const int rc = (int)cudaFuncSetAttribute(
                 kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (rc) return rc;
         }
-        MLS_LAUNCH(kernel, dim3(n_tokens), dim3(SC_THREADS), smem, stream, proj, bias, conv_w,
+        MLS_LAUNCH(kernel, dim3(n_tokens), dim3(threads), smem, stream, proj, bias, conv_w,
                    taps, q_norm, k_norm, w_dtype, eps, tail, tail_stride, state_slot, cu_q,
                    req_of_token, positions, freq, rot_dims, (__nv_bfloat16*)q_out, q_row, slot_map,
                    (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, block_size, pool_slots,
                    n_tokens, n_heads, n_kv, hd, writes, status);
     } else {
-        auto kernel = qk_conv_norm_rope_store_kernel<float>;
+        auto kernel = vec4 ? qk_conv_norm_rope_store_vec4_kernel<float>
+                           : qk_conv_norm_rope_store_kernel<float>;
         if (smem > 48 * 1024) {
             const int rc = (int)cudaFuncSetAttribute(
                 kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (rc) return rc;
         }
-        MLS_LAUNCH(kernel, dim3(n_tokens), dim3(SC_THREADS), smem, stream, proj, bias, conv_w,
+        MLS_LAUNCH(kernel, dim3(n_tokens), dim3(threads), smem, stream, proj, bias, conv_w,
                    taps, q_norm, k_norm, w_dtype, eps, tail, tail_stride, state_slot, cu_q,
                    req_of_token, positions, freq, rot_dims, (float*)q_out, q_row, slot_map,
                    (float*)k_pool, (float*)v_pool, block_size, pool_slots, n_tokens, n_heads,
