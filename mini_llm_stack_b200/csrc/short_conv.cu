@@ -26,14 +26,33 @@
 namespace {
 constexpr int SC_THREADS = 256;
 
+// The projection may come as the parts of a product cut along K (float32 [parts][T][C],
+// `stride` elements apart): their sum in the order of the parts is the product.
+__device__ __forceinline__ float proj_at(const float* __restrict__ proj, size_t i, int n_parts,
+                                         size_t stride) {
+    float s = proj[i];
+    for (int k = 1; k < n_parts; ++k) s += proj[i + (size_t)k * stride];
+    return s;
+}
+__device__ __forceinline__ float4 proj4_at(const float* __restrict__ proj, size_t i, int n_parts,
+                                           size_t stride) {
+    float4 s = *reinterpret_cast<const float4*>(proj + i);
+    for (int k = 1; k < n_parts; ++k) {
+        const float4 x = *reinterpret_cast<const float4*>(proj + i + (size_t)k * stride);
+        s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
+    }
+    return s;
+}
+
 // u_(i) of channel c for the step index i of request rows [row0, ...): from the step's
 // rows if i >= 0, else from the tail (i = -1 is the newest tail row).
-__device__ __forceinline__ float conv_input(const float* __restrict__ proj, int width, int col,
+__device__ __forceinline__ float conv_input(const float* __restrict__ proj, int n_parts,
+                                            size_t part_stride, int width, int col,
                                             const void* __restrict__ bias, int w_dtype,
                                             const float* __restrict__ tail, int n_tail,
                                             int channels, int c, int row0, int i) {
     if (i >= 0) {
-        float v = proj[(size_t)(row0 + i) * width + col];
+        float v = proj_at(proj, (size_t)(row0 + i) * width + col, n_parts, part_stride);
         if (bias) v += load_as_float(bias, c, w_dtype);
         return v;
     }
@@ -43,10 +62,11 @@ __device__ __forceinline__ float conv_input(const float* __restrict__ proj, int 
 template <typename T>
 __global__ void __launch_bounds__(SC_THREADS)
 qk_conv_norm_rope_store_kernel(
-        const float* __restrict__ proj, const void* __restrict__ bias,
+        const float* __restrict__ proj, int n_parts, long long part_stride,
+        const void* __restrict__ bias,
         const void* __restrict__ conv_w, int taps, const void* __restrict__ q_norm,
         const void* __restrict__ k_norm, int w_dtype, float eps,
-        const float* __restrict__ tail, long long tail_stride,
+        float* __restrict__ tail, long long tail_stride, int move_tail,
         const int* __restrict__ state_slot, const int* __restrict__ cu_q,
         const int* __restrict__ req_of_token, const int* __restrict__ positions,
         const double* __restrict__ freq, int rot_dims,
@@ -65,7 +85,7 @@ qk_conv_norm_rope_store_kernel(
     chain_wait();
     const int r = req_of_token[t], row0 = cu_q[r], i_t = t - row0, p = positions[t];
     const int n_tail = taps - 1;
-    const float* my_tail = n_tail > 0 ? tail + (size_t)state_slot[r] * tail_stride : nullptr;
+    float* my_tail = n_tail > 0 ? tail + (size_t)state_slot[r] * tail_stride : nullptr;
     if (threadIdx.x < rot_dims / 2)
         angle_cos_sin(p, freq[threadIdx.x], cs[threadIdx.x], cs[rot_dims / 2 + threadIdx.x]);
     float ssq = 0.f, ssk = 0.f;
@@ -73,12 +93,18 @@ qk_conv_norm_rope_store_kernel(
         float acc;
         if (n_tail > 0) {
             acc = 0.f;
-            for (int j = 0; j < taps; ++j)
-                acc = fmaf(load_as_float(conv_w, (size_t)c * taps + j, w_dtype),
-                           conv_input(proj, channels, c, bias, w_dtype, my_tail, n_tail, channels,
-                                      c, row0, i_t - n_tail + j), acc);
+            for (int j = 0; j < taps; ++j) {
+                const float u = conv_input(proj, n_parts, (size_t)part_stride, channels, c, bias,
+                                           w_dtype, my_tail, n_tail, channels, c, row0,
+                                           i_t - n_tail + j);
+                acc = fmaf(load_as_float(conv_w, (size_t)c * taps + j, w_dtype), u, acc);
+                // a step of one token a request moves its tail on itself: row j - 1 was read
+                // by this thread one tap ago
+                if (move_tail && j >= 1) my_tail[(size_t)(j - 1) * channels + c] = u;
+            }
         } else {
-            acc = conv_input(proj, channels, c, bias, w_dtype, nullptr, 0, channels, c, row0, i_t);
+            acc = conv_input(proj, n_parts, (size_t)part_stride, channels, c, bias, w_dtype, nullptr,
+                             0, channels, c, row0, i_t);
             if (taps == 1) acc *= load_as_float(conv_w, c, w_dtype);
         }
         y[c] = acc;
@@ -161,10 +187,11 @@ constexpr int QK_MAX_TAPS = 8;
 template <typename T>
 __global__ void __launch_bounds__(SC_THREADS)
 qk_conv_norm_rope_store_vec4_kernel(
-        const float* __restrict__ proj, const void* __restrict__ bias,
+        const float* __restrict__ proj, int n_parts, long long part_stride,
+        const void* __restrict__ bias,
         const void* __restrict__ conv_w, int taps, const void* __restrict__ q_norm,
         const void* __restrict__ k_norm, int w_dtype, float eps,
-        const float* __restrict__ tail, long long tail_stride,
+        float* __restrict__ tail, long long tail_stride, int move_tail,
         const int* __restrict__ state_slot, const int* __restrict__ cu_q,
         const int* __restrict__ req_of_token, const int* __restrict__ positions,
         const double* __restrict__ freq, int rot_dims,
@@ -183,7 +210,7 @@ qk_conv_norm_rope_store_vec4_kernel(
     chain_wait();
     const int r = req_of_token[t], i_t = t - cu_q[r], p = positions[t];
     const int n_tail = taps > 0 ? taps - 1 : 0;
-    const float* my_tail = n_tail > 0 ? tail + (size_t)state_slot[r] * tail_stride : nullptr;
+    float* my_tail = n_tail > 0 ? tail + (size_t)state_slot[r] * tail_stride : nullptr;
     if (threadIdx.x < half)
         angle_cos_sin(p, freq[threadIdx.x], cs[threadIdx.x], cs[half + threadIdx.x]);
     float ssq = 0.f, ssk = 0.f;
@@ -193,7 +220,7 @@ qk_conv_norm_rope_store_vec4_kernel(
         if (bias) b = load_four(bias, c, w_dtype);
         float acc[4];
         if (taps == 0) {
-            const float4 x = *reinterpret_cast<const float4*>(proj + (size_t)t * channels + c);
+            const float4 x = proj4_at(proj, (size_t)t * channels + c, n_parts, (size_t)part_stride);
             acc[0] = x.x + b.v[0]; acc[1] = x.y + b.v[1]; acc[2] = x.z + b.v[2]; acc[3] = x.w + b.v[3];
         } else {
             acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
@@ -203,11 +230,14 @@ qk_conv_norm_rope_store_vec4_kernel(
                     const int i = i_t - n_tail + j;
                     float4 x;
                     if (i >= 0) {
-                        x = *reinterpret_cast<const float4*>(proj + (size_t)(t - n_tail + j) * channels + c);
+                        x = proj4_at(proj, (size_t)(t - n_tail + j) * channels + c, n_parts,
+                                     (size_t)part_stride);
                         x.x += b.v[0]; x.y += b.v[1]; x.z += b.v[2]; x.w += b.v[3];
                     } else {
                         x = *reinterpret_cast<const float4*>(my_tail + (size_t)(n_tail + i) * channels + c);
                     }
+                    if (move_tail && j >= 1)     // (row j - 1 was read by this thread one tap ago)
+                        *reinterpret_cast<float4*>(my_tail + (size_t)(j - 1) * channels + c) = x;
                     const size_t wj = (size_t)c * taps + j;          // [channel][tap]
                     acc[0] = fmaf(load_as_float(conv_w, wj, w_dtype), x.x, acc[0]);
                     acc[1] = fmaf(load_as_float(conv_w, wj + taps, w_dtype), x.y, acc[1]);
@@ -274,7 +304,7 @@ qk_conv_norm_rope_store_vec4_kernel(
 template <typename T>
 __global__ void __launch_bounds__(SC_THREADS)
 token_shift_mix_kernel(const T* __restrict__ h, const void* __restrict__ mu, int w_dtype,
-                       int n_mix, const float* __restrict__ tail, long long tail_stride,
+                       int n_mix, float* __restrict__ tail, long long tail_stride, int move_tail,
                        const int* __restrict__ state_slot, const int* __restrict__ cu_q,
                        const int* __restrict__ req_of_token, T* __restrict__ out,
                        float* __restrict__ out_f32, int n_tokens, int d) {
@@ -283,7 +313,7 @@ token_shift_mix_kernel(const T* __restrict__ h, const void* __restrict__ mu, int
     const int t = blockIdx.x;
     const int r = req_of_token[t];
     const bool first = t == cu_q[r];
-    const float* prev_tail = tail + (size_t)state_slot[r] * tail_stride;
+    float* prev_tail = tail + (size_t)state_slot[r] * tail_stride;
     for (int c = threadIdx.x; c < d; c += SC_THREADS) {
         const float cur = Elem<T>::load(h + (size_t)t * d + c);
         const float prev = first ? prev_tail[c] : Elem<T>::load(h + (size_t)(t - 1) * d + c);
@@ -294,6 +324,8 @@ token_shift_mix_kernel(const T* __restrict__ h, const void* __restrict__ mu, int
             if (s == n_mix - 1 && out_f32) out_f32[(size_t)t * d + c] = v;
             else Elem<T>::store(out + ((size_t)s * n_tokens + t) * d + c, v);
         }
+        // a step of one token a request: this row is the next step's previous row
+        if (move_tail) prev_tail[c] = cur;
     }
 }
 
@@ -330,21 +362,23 @@ tail_update_kernel(const T* __restrict__ src, int width, int col0, const void* _
 }  // namespace
 
 MLS_API int mls_qk_conv_norm_rope_store(
-        const float* proj, const void* bias, const void* conv_w, int taps, const void* q_norm,
-        const void* k_norm, int w_dtype, float eps, const float* tail, long long tail_stride,
+        const float* proj, int n_parts, long long part_stride, const void* bias,
+        const void* conv_w, int taps, const void* q_norm, const void* k_norm, int w_dtype,
+        float eps, float* tail, long long tail_stride, int move_tail,
         const int* state_slot, const int* cu_q, const int* req_of_token, const int* positions,
         const double* freq, int rot_dims, void* q_out, int q_row, int act_dtype,
         const int* slot_map, void* k_pool, void* v_pool, int block_size, long long pool_slots,
         int n_tokens, int n_heads, int n_kv, int hd, int writes, int* status,
         cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    if (n_parts < 1) n_parts = 1;
     if (taps < 0 || taps > QK_MAX_TAPS || (taps > 1 && !tail) || rot_dims < 0 || rot_dims > hd || (rot_dims & 1) ||
         rot_dims / 2 > SC_THREADS || (rot_dims > 0 && !freq))
         return MLS_ERR_UNSUPPORTED;
     const size_t smem = ((size_t)(n_heads + n_kv) * hd + rot_dims) * sizeof(float);
     if (smem > 200 * 1024) return MLS_ERR_UNSUPPORTED;
     // four channels a thread where every row allows it (the model's sizes alone decide)
-    const bool vec4 = (((n_heads * hd) | hd | q_row) & 3) == 0 &&
+    const bool vec4 = (((n_heads * hd) | hd | q_row) & 3) == 0 && (part_stride & 3) == 0 &&
                       (taps <= 1 || (tail_stride & 3) == 0);
     // (the block's shape depends on the model's sizes alone, and with it the order of the sums)
     const int threads = (vec4 && (n_heads + n_kv) * hd <= 4096 && rot_dims / 2 <= 128) ? 128 : SC_THREADS;
@@ -356,8 +390,8 @@ MLS_API int mls_qk_conv_norm_rope_store(
                 kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (rc) return rc;
         }
-        MLS_LAUNCH(kernel, dim3(n_tokens), dim3(threads), smem, stream, proj, bias, conv_w,
-                   taps, q_norm, k_norm, w_dtype, eps, tail, tail_stride, state_slot, cu_q,
+        MLS_LAUNCH(kernel, dim3(n_tokens), dim3(threads), smem, stream, proj, n_parts, part_stride, bias,
+                   conv_w, taps, q_norm, k_norm, w_dtype, eps, tail, tail_stride, move_tail, state_slot, cu_q,
                    req_of_token, positions, freq, rot_dims, (__nv_bfloat16*)q_out, q_row, slot_map,
                    (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, block_size, pool_slots,
                    n_tokens, n_heads, n_kv, hd, writes, status);
@@ -369,8 +403,8 @@ MLS_API int mls_qk_conv_norm_rope_store(
                 kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (rc) return rc;
         }
-        MLS_LAUNCH(kernel, dim3(n_tokens), dim3(threads), smem, stream, proj, bias, conv_w,
-                   taps, q_norm, k_norm, w_dtype, eps, tail, tail_stride, state_slot, cu_q,
+        MLS_LAUNCH(kernel, dim3(n_tokens), dim3(threads), smem, stream, proj, n_parts, part_stride, bias,
+                   conv_w, taps, q_norm, k_norm, w_dtype, eps, tail, tail_stride, move_tail, state_slot, cu_q,
                    req_of_token, positions, freq, rot_dims, (float*)q_out, q_row, slot_map,
                    (float*)k_pool, (float*)v_pool, block_size, pool_slots, n_tokens, n_heads,
                    n_kv, hd, writes, status);
@@ -379,7 +413,7 @@ MLS_API int mls_qk_conv_norm_rope_store(
 }
 
 MLS_API int mls_token_shift_mix(const void* h, int act_dtype, const void* mu, int w_dtype,
-                                int n_mix, const float* tail, long long tail_stride,
+                                int n_mix, float* tail, long long tail_stride, int move_tail,
                                 const int* state_slot, const int* cu_q, const int* req_of_token,
                                 void* out, float* out_f32, int n_tokens, int d,
                                 cudaStream_t stream) {
@@ -387,10 +421,10 @@ MLS_API int mls_token_shift_mix(const void* h, int act_dtype, const void* mu, in
     if (act_dtype == MLS_BF16)
         MLS_LAUNCH((token_shift_mix_kernel<__nv_bfloat16>), dim3(n_tokens), dim3(SC_THREADS), 0,
                    stream, (const __nv_bfloat16*)h, mu, w_dtype, n_mix, tail, tail_stride,
-                   state_slot, cu_q, req_of_token, (__nv_bfloat16*)out, out_f32, n_tokens, d);
+                   move_tail, state_slot, cu_q, req_of_token, (__nv_bfloat16*)out, out_f32, n_tokens, d);
     else
         MLS_LAUNCH((token_shift_mix_kernel<float>), dim3(n_tokens), dim3(SC_THREADS), 0, stream,
-                   (const float*)h, mu, w_dtype, n_mix, tail, tail_stride, state_slot, cu_q,
+                   (const float*)h, mu, w_dtype, n_mix, tail, tail_stride, move_tail, state_slot, cu_q,
                    req_of_token, (float*)out, out_f32, n_tokens, d);
     return launch_status();
 }

@@ -725,10 +725,11 @@ class Ops:
                                     [_P, _I, _P, _I, _P, _I, _I, _I, _P])}
         elif name == "shortconv":
             fns = {"qk": _decl(lib, "mls_qk_conv_norm_rope_store",
-                               [_P, _P, _P, _I, _P, _P, _I, _F, _P, _LL, _P, _P, _P, _P, _P, _I,
-                                _P, _I, _I, _P, _P, _P, _I, _LL, _I, _I, _I, _I, _I, _P, _P]),
+                               [_P, _I, _LL, _P, _P, _I, _P, _P, _I, _F, _P, _LL, _I, _P, _P, _P, _P,
+                                _P, _I, _P, _I, _I, _P, _P, _P, _I, _LL, _I, _I, _I, _I, _I, _P, _P]),
                    "shift_mix": _decl(lib, "mls_token_shift_mix",
-                                      [_P, _I, _P, _I, _I, _P, _LL, _P, _P, _P, _P, _P, _I, _I, _P]),
+                                      [_P, _I, _P, _I, _I, _P, _LL, _I, _P, _P, _P, _P, _P, _I, _I,
+                                       _P]),
                    "tail": _decl(lib, "mls_tail_update",
                                  [_P, _I, _I, _I, _P, _I, _P, _LL, _I, _I, _P, _P, _I, _P])}
         elif name == "scan":
@@ -973,13 +974,15 @@ class Ops:
 
     def qk_conv_norm_rope_store(self, proj, bias, conv_w, taps: int, q_norm, k_norm, eps: float,
                                 tail, freq, rot_dims: int, q_out, cache, step, n_heads: int,
-                                n_kv: int, hd: int) -> None:
+                                n_kv: int, hd: int, parts=None, move_tail: bool = False) -> None:
         """From the float32 projection ``proj [T, (H + G) * hd]`` (q heads, then k heads):
         add ``bias``, convolve every channel over time (``conv_w [C, taps]``; the inputs
         before the step come from ``tail [slots, (taps - 1) * C]``), store the convolved k
         as the values, RMS-normalise the whole q row and the whole k row, rotate the first
         ``rot_dims`` entries of every head (2i with 2i + 1, ``freq`` float64), write q into
-        ``q_out`` and k into the pages.  ``mls_tail_update`` moves the tail on afterwards."""
+        ``q_out`` and k into the pages.  ``tail_update`` moves the tail on afterwards, or,
+        in a step of one token a request, this kernel itself (``move_tail``).  With ``parts``
+        (``SplitParts`` of the projection) the rows are read from there instead of ``proj``."""
         g = step.groups[cache.group]
         t = step.n_tokens
         c = (n_heads + n_kv) * hd
@@ -1001,16 +1004,26 @@ class Ops:
               "qk_conv_norm_rope_store: bad tail")
         _need(rot_dims == 0 or (freq.dtype == torch.float64 and freq.numel() == rot_dims // 2),
               "qk_conv_norm_rope_store: bad frequencies")
+        _need(not move_tail or step.max_q_len == 1,
+              "qk_conv_norm_rope_store: the tail moves in the kernel only in steps of single tokens")
+        src, n_parts, stride = proj.data_ptr(), 1, 0
+        if parts is not None:
+            _need(tuple(parts.shape) == (t, c) and parts.parts.is_contiguous(),
+                  "qk_conv_norm_rope_store: these parts cannot be read")
+            src, n_parts, stride = parts.parts.data_ptr(), parts.parts.shape[0], t * c
         self.launches += 1
         _check(self._part_lib("shortconv")["qk"](
-            _ptr(proj), _ptr(bias), _ptr(conv_w) if taps else None, taps, _ptr(q_norm),
+            src, n_parts, stride, _ptr(bias), _ptr(conv_w) if taps else None, taps, _ptr(q_norm),
             _ptr(k_norm), _code(q_norm.dtype), float(eps), _ptr(tail) if taps > 1 else None,
-            tail.stride(0) if taps > 1 else 0, _ptr(step.state_slot), _ptr(step.cu_q),
+            tail.stride(0) if taps > 1 else 0, 1 if (move_tail and taps > 1) else 0,
+            _ptr(step.state_slot), _ptr(step.cu_q),
             _ptr(step.req_of_token), _ptr(step.positions), _ptr(freq) if rot_dims else None,
             rot_dims, _ptr(q_out), q_out.shape[1], _code(pool.dtype), _ptr(g.slot_map), _ptr(pool),
             _ptr(cache.v_pool), g.block_size, pool.shape[1] * pool.shape[2], t, n_heads, n_kv, hd,
             1 if cache.writes else 0, _ptr(self.status), self._stream()),
             "qk_conv_norm_rope_store")
+        if parts is not None:
+            parts.release()
 
     def tail_update(self, src, col0: int, channels: int, bias, tail, n_tail: int, step) -> None:
         """``tail [slots, n_tail * channels]`` (float32, oldest row first) becomes the last
@@ -1029,11 +1042,12 @@ class Ops:
             channels, _ptr(step.state_slot), _ptr(step.cu_q), step.n_requests, self._stream()),
             "tail_update")
 
-    def token_shift_mix(self, h, mu, prev, out, out_f32, step) -> None:
+    def token_shift_mix(self, h, mu, prev, out, out_f32, step, move_tail: bool = False) -> None:
         """``mix_s[t] = h[t] + (h[t - 1] - h[t]) * mu[s]`` for every row s of ``mu [n, d]``,
         with a request's row before its first of the step from ``prev [slots, d]``
         (float32).  ``out [n or n - 1, T, d]``; with ``out_f32 [T, d]`` the last mix goes
-        there in float32."""
+        there in float32.  ``move_tail`` (steps of one token a request only): ``prev`` becomes
+        this step's rows in the same kernel."""
         t, d = h.shape
         n = mu.shape[0]
         _need(h.is_contiguous() and mu.shape == (n, d) and mu.is_contiguous(),
@@ -1044,10 +1058,12 @@ class Ops:
               and out.shape[0] >= (n - 1 if out_f32 is not None else n), "token_shift_mix: out")
         _need(out_f32 is None or (out_f32.shape == (t, d) and out_f32.dtype == torch.float32
                                   and out_f32.is_contiguous()), "token_shift_mix: float32 out")
+        _need(not move_tail or step.max_q_len == 1,
+              "token_shift_mix: the previous rows move in the kernel only in steps of single tokens")
         self.launches += 1
         _check(self._part_lib("shortconv")["shift_mix"](
             _ptr(h), _code(h.dtype), _ptr(mu), _code(mu.dtype), n, _ptr(prev), prev.stride(0),
-            _ptr(step.state_slot), _ptr(step.cu_q), _ptr(step.req_of_token), _ptr(out),
+            1 if move_tail else 0, _ptr(step.state_slot), _ptr(step.cu_q), _ptr(step.req_of_token), _ptr(out),
             _ptr(out_f32), t, d, self._stream()), "token_shift_mix")
 
     def require_scan(self, e: int) -> None:

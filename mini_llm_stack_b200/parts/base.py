@@ -15,7 +15,7 @@ Norm:
     forward(stream, rows=None) -> h               stream.settle + normalise
 Mixer:
     cache_spec() -> PagedKV | FixedState | PagedWithState | None   what it keeps per request
-    forward(h, step, cache) -> delta [T, d_model]
+    forward(h, step, cache) -> delta [T, d_model], or (delta, vector added to every row)
 FeedForward:
     forward(h, step) -> delta [T, d_model]
 PositionEncoding (rotary kind):

@@ -71,7 +71,12 @@ class PreNormBlock(Part):
     def forward(self, stream: ResidualStream, step: StepContext,
                 cache: CacheHandle) -> None:
         h = self.mixer_norm.forward(stream)
-        stream.push(self.mixer.forward(h, step, cache))
+        delta = self.mixer.forward(h, step, cache)
+        if isinstance(delta, tuple):
+            # (delta, a vector for every row): a mixer whose output projection has a bias
+            delta, vec = delta
+            stream.push_more(vec=vec)
+        stream.push(delta)
         if self.ffn is None:
             return
         h = self.ffn_norm.forward(stream)

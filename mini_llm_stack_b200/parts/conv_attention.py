@@ -96,20 +96,26 @@ class ConvKeyAttention(Mixer):
         rt, ops = self.runtime, self.runtime.ops
         t, hd = step.n_tokens, self.head_dim
         proj = rt.buffer("qk_proj", (t, self.channels), torch.float32)
-        ops.linear(h, self.w_qk, proj)
+        # a step of one token a request: the product may stay in the parts it was cut into
+        # along K (the kernel below adds them up), and that kernel moves the tail on itself
+        single = step.max_q_len == 1
+        src = ops.linear_parts(h, self.w_qk, proj) if single else None
+        if src is None:
+            ops.linear(h, self.w_qk, proj)
         # the attention kernels read a row of [q heads | k heads | v heads]; only q is there
         q_row = rt.buffer("qkv", (t, (self.n_heads + 2 * self.n_kv_heads) * hd), rt.act_dtype)
         pos = self.position
         ops.qk_conv_norm_rope_store(proj, self.b_qk, self.conv, self.taps, self.g_q, self.g_k,
                                     self.eps, cache.state, pos.freq if pos else None,
                                     pos.dims if pos else 0, q_row, cache, step, self.n_heads,
-                                    self.n_kv_heads, hd)
-        if self.taps > 1 and cache.writes:
+                                    self.n_kv_heads, hd,
+                                    parts=src if (src is not None and src is not proj) else None,
+                                    move_tail=single and cache.writes)
+        if self.taps > 1 and cache.writes and not single:
             ops.tail_update(proj, 0, self.channels, self.b_qk, cache.state, self.taps - 1, step)
         o = rt.buffer("attn_out", (t, self.n_heads * hd), rt.act_dtype)
         ops.paged_attention(q_row, o, cache, step, self.n_heads, self.n_kv_heads, hd, self.scale,
                             self.window or 0, plan=self.plan(step), softcap=self.softcap)
+        # the output bias goes to the stream beside the product (which may stay in its K-parts)
         delta = rt.buffer("delta_f32", (t, self.d_model), torch.float32)
-        ops.linear(o, self.w_o, delta)
-        ops.residual_add(delta, None, self.b_o)
-        return delta
+        return ops.linear_parts(o, self.w_o, delta), self.b_o

@@ -85,8 +85,10 @@ class WkvMixer(Mixer):
         prev = cache.state[:, s_floats:s_floats + d]
         mixes = rt.buffer("wkv_mix", (4, t, d), rt.act_dtype)
         mix_w = rt.buffer("wkv_mix_w", (t, d), torch.float32)
-        ops.token_shift_mix(h, self.mu, prev, mixes, mix_w, step)
-        ops.tail_update(h, 0, d, None, prev, 1, step)
+        single = step.max_q_len == 1          # then the kernel moves the previous rows on itself
+        ops.token_shift_mix(h, self.mu, prev, mixes, mix_w, step, move_tail=single)
+        if not single:
+            ops.tail_update(h, 0, d, None, prev, 1, step)
         if 4 * t <= self.STACK_ROWS and self.w_all.dtype == torch.bfloat16:
             # few tokens: the step streams weights, so one product of all four mixes with
             # all four matrices (of whose sixteen blocks four are wanted) beats four products
