@@ -36,12 +36,8 @@ __device__ __forceinline__ float proj_at(const float* __restrict__ proj, size_t 
 }
 __device__ __forceinline__ float4 proj4_at(const float* __restrict__ proj, size_t i, int n_parts,
                                            size_t stride) {
-    float4 s = *reinterpret_cast<const float4*>(proj + i);
-    for (int k = 1; k < n_parts; ++k) {
-        const float4 x = *reinterpret_cast<const float4*>(proj + i + (size_t)k * stride);
-        s.x += x.x; s.y += x.y; s.z += x.z; s.w += x.w;
-    }
-    return s;
+    if (n_parts == 1) return *reinterpret_cast<const float4*>(proj + i);
+    return sum_parts4<4>(proj, i, n_parts, stride);      // four parts' loads under way at a time
 }
 
 // u_(i) of channel c for the step index i of request rows [row0, ...): from the step's
@@ -185,7 +181,7 @@ __device__ __forceinline__ void store_four<__nv_bfloat16>(__nv_bfloat16* dst, co
 constexpr int QK_MAX_TAPS = 8;
 
 template <typename T>
-__global__ void __launch_bounds__(SC_THREADS)
+__global__ void __launch_bounds__(SC_THREADS, 3)
 qk_conv_norm_rope_store_vec4_kernel(
         const float* __restrict__ proj, int n_parts, long long part_stride,
         const void* __restrict__ bias,
