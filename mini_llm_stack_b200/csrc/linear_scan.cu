@@ -274,7 +274,8 @@ decay_lowrank_kernel(const float* __restrict__ lo, int rank, const float* __rest
     float z[DL_TOKENS];
 #pragma unroll
     for (int tt = 0; tt < DL_TOKENS; ++tt) z[tt] = 0.f;
-    for (int i = 0; i < rank; ++i) {
+#pragma unroll 8
+    for (int i = 0; i < rank; ++i) {                     // (eight loads under way; the sums stay in order)
         const float w = w2t[(size_t)i * channels + c];
 #pragma unroll
         for (int tt = 0; tt < DL_TOKENS; ++tt)

@@ -310,6 +310,7 @@ token_shift_mix_kernel(const T* __restrict__ h, const void* __restrict__ mu, int
     const int r = req_of_token[t];
     const bool first = t == cu_q[r];
     float* prev_tail = tail + (size_t)state_slot[r] * tail_stride;
+#pragma unroll 4
     for (int c = threadIdx.x; c < d; c += SC_THREADS) {
         const float cur = Elem<T>::load(h + (size_t)t * d + c);
         const float prev = first ? prev_tail[c] : Elem<T>::load(h + (size_t)(t - 1) * d + c);
