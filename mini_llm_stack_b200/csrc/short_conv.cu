@@ -369,13 +369,14 @@ MLS_API int mls_qk_conv_norm_rope_store(
         cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_parts < 1) n_parts = 1;
-    if (taps < 0 || taps > QK_MAX_TAPS || (taps > 1 && !tail) || rot_dims < 0 || rot_dims > hd || (rot_dims & 1) ||
+    if (taps < 0 || (taps > 1 && !tail) || rot_dims < 0 || rot_dims > hd || (rot_dims & 1) ||
         rot_dims / 2 > SC_THREADS || (rot_dims > 0 && !freq))
         return MLS_ERR_UNSUPPORTED;
     const size_t smem = ((size_t)(n_heads + n_kv) * hd + rot_dims) * sizeof(float);
     if (smem > 200 * 1024) return MLS_ERR_UNSUPPORTED;
     // four channels a thread where every row allows it (the model's sizes alone decide)
     const bool vec4 = (((n_heads * hd) | hd | q_row) & 3) == 0 && (part_stride & 3) == 0 &&
+                      taps <= QK_MAX_TAPS &&
                       (taps <= 1 || (tail_stride & 3) == 0);
     // (the block's shape depends on the model's sizes alone, and with it the order of the sums)
     const int threads = (vec4 && (n_heads + n_kv) * hd <= 4096 && rot_dims / 2 <= 128) ? 128 : SC_THREADS;

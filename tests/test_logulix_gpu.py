@@ -348,6 +348,12 @@ ONE_LAYER = {
         "mixer": L.attention(3, 1, 8, 0.5, conv=4, window=16, rot=L.rot(8, 50.0))},
     "attention_conv2_window1": {"type": "attention", "mlp": None,
                                 "mixer": L.attention(2, 1, 16, 0.5, conv=2, window=1, softcap=2.0)},
+    # more taps than the four-channel kernel unrolls, and a head size it does not take
+    "attention_conv9_head_6": {"type": "attention", "mlp": None,
+                               "mixer": L.attention(2, 2, 6, 0.5, conv=9, window=12,
+                                                    rot=L.rot(4, 20.0))},
+    "attention_conv9_head_16": {"type": "attention", "mlp": None,
+                                "mixer": L.attention(2, 1, 16, 0.4, conv=9, rot=L.rot(16, 20.0))},
     "attention_conv1": {"type": "attention", "mlp": None,
                         "mixer": L.attention(1, 1, 32, 0.2, conv=1, window=40, softcap=50.0)},
     "attention_head_80": {"type": "attention", "mlp": None,
