@@ -75,6 +75,7 @@ def models(tmp_path_factory):
     out = {}
     for key, raw, patch in (("mixed", L.L_MIXED, None), ("plain", L.L_PLAIN, None),
                             ("wide", L.L_WIDE, None), ("states", L.L_STATES, long_memory),
+                            ("edge", L.L_EDGE, None),
                             ("sharp", L.L_WIDE, both(sharp(4.0), long_memory))):
         for dtype in ("float32", "bfloat16"):
             folder = tmp / f"{key}_{dtype}"
@@ -425,7 +426,7 @@ def test_a_window_one_token_off_would_show(tmp_path, window, dtype):
 
 # ------------------------------------------------------------------- whole models
 LENGTHS = {"mixed": [1, 2, 19, 150], "plain": [1, 33, 97], "wide": [3, 64, 260],
-           "sharp": [5, 300], "states": [1, 2, 170]}
+           "sharp": [5, 300], "states": [1, 2, 170], "edge": [1, 7, 60]}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -108,6 +108,20 @@ L_STATES = {
 }
 
 
+# an attention layer without a feed-forward right before the repeated run (its output bias
+# still waits on the stream when the pass begins), one pass only, retention after the run
+L_EDGE = {
+    "architecture": "Logulix", "vocab": 71, "width": 32, "norm": {"eps": 1e-6},
+    "embedding": {"scale": 2.0}, "loop": {"start": 1, "stop": 2, "times": 1},
+    "layers": [
+        {"type": "attention", "mlp": None,
+         "mixer": attention(2, 2, 8, 0.35, conv=3, window=5, rot=rot(8, 40.0), softcap=4.0)},
+        {"type": "wkv", "mixer": wkv(2, 16, 3), "mlp": None},
+        {"type": "retention", "mixer": retention(4, 4, 12, [0.7, 0.8, 0.9, 0.95]), "mlp": dense(48)},
+    ],
+}
+
+
 def one_layer(layer: dict, width: int = 40, vocab: int = 61, eps: float = 1e-5) -> dict:
     """A model of the embedding, one layer, the final norm and the head."""
     return {"architecture": "Logulix", "vocab": vocab, "width": width, "norm": {"eps": eps},
