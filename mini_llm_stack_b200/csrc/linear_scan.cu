@@ -45,8 +45,10 @@ __device__ __forceinline__ float4 load4(const void* base, int dtype, size_t i) {
     return *reinterpret_cast<const float4*>((const float*)base + i);
 }
 
+// (Four CTAs an SM up to 16 rows a thread: 592 places, so that the 512 CTAs of 32 heads with
+// 256 value columns are one round and not two.)
 template <int RPT, bool TOK_DECAY>
-__global__ void __launch_bounds__(LS_THREADS)
+__global__ void __launch_bounds__(LS_THREADS, RPT <= 16 ? 4 : 2)
 linear_scan_kernel(const void* __restrict__ a_src, int a_dtype, int a_row, int a_off,
                    const void* __restrict__ k_src, int k_dtype, int k_row, int k_off,
                    const void* __restrict__ v_src, int v_dtype, int v_row, int v_off,
